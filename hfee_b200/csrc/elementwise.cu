@@ -1,0 +1,207 @@
+// Embedding gather, RMSNorm, rotary table, rotary + cache write, SwiGLU.
+// All arithmetic is float32 (the rotary table is built in float64); T is the
+// storage type of activations, weights tables and cache pages.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[i,:] = table[token_i,:] as float32 (the residual stream is float32).
+// Reference: x[i,:] = embed.Row(tokens[i]), hostfog/hfee internal/llm/forward.go:75-77.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int width, int vocab) {
+  int i = blockIdx.x;
+  int tok = tokens[i];
+  bool ok = tok >= 0 && tok < vocab;
+  const T* row = table + (long long)(ok ? tok : 0) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(long long)i * width + c] = ok ? to_f32<T>(row[c]) : 0.f;
+}
+
+HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, float* out, int n,
+                        int width, int vocab, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d vocab=%d", n, width, vocab);
+  int threads = width >= 256 ? 256 : 64;
+  if (dtype == HFEE_F32)
+    embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, out, width, vocab);
+  else if (dtype == HFEE_BF16)
+    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, width, vocab);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "embed: unknown dtype %d", dtype);
+  return hfee_check_launch("embed");
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// out[r,:] = x[row(r),:] * rsqrt(mean(x^2) + eps) * w, one block per row, float32 math
+// with a fixed reduction order (so a row's result does not depend on the batch).
+// `rows` (optional) gathers: row(r) = rows[r].  `add_unit` uses (1 + w).
+// Reference: internal/ggml/ops.go:125-134 (order (x*scale)*w).
+template <typename TOut, int THREADS>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ rows, TOut* __restrict__ out, int width,
+                               float eps, int add_unit) {
+  __shared__ float partial[THREADS / 32];
+  int r = blockIdx.x;
+  const float* xr = x + (long long)(rows ? rows[r] : r) * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += THREADS) {
+    float v = xr[c];
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) total += partial[i];
+  float scale = 1.0f / sqrtf(total / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += THREADS) {
+    float wv = add_unit ? 1.f + w[c] : w[c];
+    out[(long long)r * width + c] = from_f32<TOut>(xr[c] * scale * wv);
+  }
+}
+
+HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
+                          int n, int width, float eps, int add_unit, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && width > 0, "rmsnorm: bad sizes n=%d width=%d", n, width);
+  if (out_dtype == HFEE_F32)
+    rmsnorm_kernel<float, 256><<<n, 256, 0, stream>>>(x, w, rows, (float*)out, width, eps, add_unit);
+  else if (out_dtype == HFEE_BF16)
+    rmsnorm_kernel<__nv_bfloat16, 256><<<n, 256, 0, stream>>>(x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
+  return hfee_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------- rotary table
+// cs[i, j] = (cos, sin)(positions[i] * inv_freq[j]) evaluated in float64, stored
+// as float32; built once per step and shared by every layer with the same
+// rotary parameters.  Reference: math.Sincos(float64(pos) * invFreq[i]),
+// internal/llm/forward.go:185-186.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int n, int half) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * half) return;
+  int i = idx / half, j = idx % half;
+  double s, c;
+  sincos((double)positions[i] * inv_freq[j], &s, &c);
+  cs[idx] = make_float2((float)c, (float)s);
+}
+
+HFEE_API int hfee_rope_table(const int* positions, const double* inv_freq, float* cs, int n, int half,
+                             cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && half > 0, "rope_table: bad sizes n=%d half=%d", n, half);
+  int total = n * half;
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)cs, n, half);
+  return hfee_check_launch("rope_table");
+}
+
+// ---------------------------------------------------------------- rotary + cache write
+// Input rows hold [q heads | k heads | v heads] (the fused projection).  Rotates q
+// into q_out and k into the cache page of (slot, position); copies v to its page.
+// `cs` may be null (no rotation).  Pair (i, i+rope_dim/2) when `interleaved` is 0,
+// (2i, 2i+1) otherwise; dims at or above rope_dim pass through.  k/v pools may be
+// null when this layer reads another layer's cache (q only).
+// Reference: internal/llm/forward.go:90-102,181-196.
+template <typename T>
+__global__ void rope_cache_kernel(const T* __restrict__ qkv, int ld_qkv, const float2* __restrict__ cs,
+                                  const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                                  T* __restrict__ q_out, int ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                  PagedCache cache, int heads, int rope_dim, int interleaved) {
+  int i = blockIdx.x;
+  int hd = cache.head_dim, kvh = cache.kv_heads;
+  int half = rope_dim / 2;
+  int pos = positions[i];
+  int slot = slot_of_token[i];
+  const T* row = qkv + (long long)i * ld_qkv;
+  int total_heads = k_pool ? heads + 2 * kvh : heads;   // q only when this run reads another run's cache
+  // one work item = (head, pair index within the head); hd/2 items per head
+  int per_head = hd / 2;
+  for (int w = threadIdx.x; w < total_heads * per_head; w += blockDim.x) {
+    int h = w / per_head, p = w % per_head;
+    const T* src = row + (long long)h * hd;
+    int a, b;
+    bool rotate = cs != nullptr && h < heads + kvh;
+    if (p < half) {
+      a = interleaved ? 2 * p : p;
+      b = interleaved ? 2 * p + 1 : p + half;
+    } else {                       // unrotated tail of a partial rotary head
+      a = rope_dim + 2 * (p - half);
+      b = a + 1;
+      rotate = false;
+    }
+    float x0 = to_f32<T>(src[a]), x1 = to_f32<T>(src[b]);
+    float y0 = x0, y1 = x1;
+    if (rotate) {
+      float2 t = cs[(long long)i * half + p];
+      y0 = x0 * t.x - x1 * t.y;
+      y1 = x0 * t.y + x1 * t.x;
+    }
+    T* dst;
+    if (h < heads) {
+      dst = q_out + (long long)i * ld_q + (long long)h * hd;
+    } else {
+      if (k_pool == nullptr) continue;
+      int kh = h < heads + kvh ? h - heads : h - heads - kvh;
+      T* pool = h < heads + kvh ? k_pool : v_pool;
+      dst = pool + paged_offset(cache, slot, pos, kh);
+    }
+    dst[a] = from_f32<T>(y0);
+    dst[b] = from_f32<T>(y1);
+  }
+}
+
+HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs, const int* positions,
+                                   const int* slot_of_token, void* q_out, int ld_q, void* k_pool,
+                                   void* v_pool, const int* block_table, int max_pages, int page_size,
+                                   int n, int heads, int kv_heads, int head_dim, int rope_dim,
+                                   int interleaved, int dtype, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope: head_dim %d must be even", head_dim);
+  HFEE_REQUIRE(rope_dim >= 0 && rope_dim <= head_dim && rope_dim % 2 == 0,
+               "rope: rope_dim %d must be even and at most head_dim %d", rope_dim, head_dim);
+  HFEE_REQUIRE(heads > 0 && kv_heads > 0 && page_size > 0 && max_pages > 0, "rope: bad sizes");
+  PagedCache c{block_table, max_pages, page_size, kv_heads, head_dim,
+               (long long)kv_heads * page_size * head_dim};
+  int threads = 256;
+  if (dtype == HFEE_F32)
+    rope_cache_kernel<float><<<n, threads, 0, stream>>>((const float*)qkv, ld_qkv, (const float2*)cs, positions,
+        slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c, heads, rope_dim, interleaved);
+  else if (dtype == HFEE_BF16)
+    rope_cache_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
+        positions, slot_of_token, (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, c,
+        heads, rope_dim, interleaved);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "rope: unknown dtype %d", dtype);
+  return hfee_check_launch("rope_cache_write");
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// h[i, c] = silu(gu[i, c]) * gu[i, inter + c]; g / (1 + exp(-g)) * u in float32.
+// Reference: internal/ggml/ops.go:160-165.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, int ld_gu, T* __restrict__ h, int ld_h, int n, int inter) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * inter) return;
+  int i = (int)(idx / inter), c = (int)(idx % inter);
+  float g = to_f32<T>(gu[(long long)i * ld_gu + c]);
+  float u = to_f32<T>(gu[(long long)i * ld_gu + inter + c]);
+  h[(long long)i * ld_h + c] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+HFEE_API int hfee_swiglu(const void* gu, int ld_gu, void* h, int ld_h, int n, int inter, int dtype,
+                         cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && inter > 0 && ld_gu >= 2 * inter && ld_h >= inter, "swiglu: bad sizes");
+  long long total = (long long)n * inter;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == HFEE_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld_gu, (float*)h, ld_h, n, inter);
+  else if (dtype == HFEE_BF16)
+    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "swiglu: unknown dtype %d", dtype);
+  return hfee_check_launch("swiglu");
+}

@@ -1,0 +1,89 @@
+// Next-token choice on the device over float32 logits [M, V]: argmax where a
+// row's temperature is <= 0 (first maximum wins), else one draw from
+// softmax(logits / T) by inverse CDF in index order with the uniform number the
+// host supplies for that row.
+// Reference: hostfog/hfee internal/llm/sampler.go:76-84 (greedy, strict '>'),
+// :88-95 (probabilities relative to the maximum, float64), :118-129 (draw).
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
+              const double* __restrict__ uniform, int* __restrict__ out) {
+  __shared__ float s_val[THREADS];
+  __shared__ int s_idx[THREADS];
+  __shared__ double s_sum[THREADS];
+  int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (long long)r * ld;
+
+  // contiguous chunk per thread so that index order is kept
+  int chunk = (V + THREADS - 1) / THREADS;
+  int begin = min(V, tid * chunk), end = min(V, begin + chunk);
+
+  float best = -INFINITY;
+  int best_i = V;          // V = "none"
+  for (int c = begin; c < end; ++c) {
+    float v = row[c];
+    if (best_i == V || v > best) { best = v; best_i = c; }
+  }
+  s_val[tid] = best;
+  s_idx[tid] = best_i;
+  __syncthreads();
+  for (int o = THREADS / 2; o > 0; o >>= 1) {
+    if (tid < o) {
+      float v2 = s_val[tid + o];
+      int i2 = s_idx[tid + o];
+      // keep the lower index on ties; an empty chunk (index V) never wins
+      if (i2 < V && (s_idx[tid] == V || v2 > s_val[tid] || (v2 == s_val[tid] && i2 < s_idx[tid]))) {
+        s_val[tid] = v2;
+        s_idx[tid] = i2;
+      }
+    }
+    __syncthreads();
+  }
+  float vmax = s_val[0];
+  int imax = s_idx[0];
+  float T = temperature ? temperature[r] : 0.f;
+  if (!(T > 0.f)) {
+    if (tid == 0) out[r] = imax;
+    return;
+  }
+
+  double local = 0.0;
+  for (int c = begin; c < end; ++c) local += exp((double)((row[c] - vmax) / T));
+  s_sum[tid] = local;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int t = 0; t < THREADS; ++t) total += s_sum[t];
+    double target = uniform[r] * total;
+    // find the chunk, then the element, where the running sum first reaches the target
+    int t = 0;
+    double run = 0.0;
+    while (t < THREADS - 1 && run + s_sum[t] < target) run += s_sum[t++];
+    int b = min(V, t * chunk), e = min(V, b + chunk);
+    int pick = imax;
+    bool found = false;
+    for (int c = b; c < e; ++c) {
+      run += exp((double)((row[c] - vmax) / T));
+      pick = c;
+      if (run >= target) { found = true; break; }
+    }
+    if (!found && e == b) pick = imax;
+    out[r] = pick;
+  }
+}
+
+}  // namespace
+
+HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const float* temperature,
+                         const double* uniform, int* out, cudaStream_t stream) {
+  if (M == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && V > 0 && ld >= V, "sample: bad sizes M=%d V=%d ld=%lld", M, V, ld);
+  HFEE_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures need uniform numbers");
+  sample_kernel<<<M, THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out);
+  return hfee_check_launch("sample");
+}

@@ -1,0 +1,88 @@
+"""The step function: runs one batch of (request, next tokens) entries through the
+model from the cache and returns the logits at the wanted places.
+
+Counterpart of ``Model.Forward([]Batch)`` in hostfog/hfee
+internal/llm/forward.go:51-142, where entries may be portions of prompts beside
+single decoded tokens; here over a paged cache and returning logits at any wanted
+token, not only the last.
+"""
+from __future__ import annotations
+
+from typing import Any, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config import EngineConfig, read_config_json, resolve
+from ..parts import DecoderModel, Runtime
+from ..weights import Checkpoint
+from .batch import Step, StepBuffers, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class ModelRunner:
+    """A loaded model with its cache: ``open()`` / ``step()`` / ``close()`` per request."""
+
+    def __init__(self, model_dir: str, engine: Optional[EngineConfig] = None):
+        self.engine = engine or EngineConfig()
+        e = self.engine
+        self.arch, self.config = resolve(read_config_json(model_dir))
+        self.spec = self.arch.build_spec(self.config)
+        self.device = torch.device(e.device)
+        self.rt = Runtime(_DTYPES[e.dtype], self.device, e.max_batch_tokens, e.max_requests, e.page_size)
+        checkpoint = Checkpoint(model_dir)
+        self.model = DecoderModel(self.spec, checkpoint, self.rt)
+        checkpoint.files.close()
+        self.cache = CacheManager(self.model.cache_needs(), e.page_size, e.num_pages, e.max_requests,
+                                  e.max_context, self.rt.dtype, self.device)
+        self.buffers = StepBuffers(e.max_batch_tokens, e.max_requests, self.device)
+        self.vocab = self.spec.vocab
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Append each entry's tokens to its request and return float32 logits
+        [sum(len(e.want)), vocab] on the device in the order of the entries and of
+        ``want`` (None if nothing is wanted).  Raises :class:`OutOfPages`, before
+        anything ran, if the cache cannot hold the new tokens."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        cache = self.cache
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.vocab:
+                raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {self.vocab}")
+            if cache.length[e.slot] + len(e.tokens) > cache.max_context:
+                raise ValueError(f"slot {e.slot}: {cache.length[e.slot] + len(e.tokens)} tokens exceed the "
+                                 f"context limit of {cache.max_context}")
+        # all or nothing: check every group's free pages against the whole step's demand
+        for g in cache.paged:
+            need = sum(cache._missing(g, e.slot, cache.length[e.slot] + len(e.tokens)) for e in entries)
+            if need > g.pool.free_pages:
+                raise OutOfPages(f"step needs {need} pages, {g.pool.free_pages} are free")
+        for e in entries:
+            cache.reserve(e.slot, cache.length[e.slot] + len(e.tokens))
+        cache.sync()
+        step = Step(entries, cache.length, self.buffers)
+        logits = self.model.forward(step, cache.views())
+        for e in entries:
+            cache.commit(e.slot, cache.length[e.slot] + len(e.tokens))
+        self.steps_run += 1
+        self.last_step = step
+        return logits

@@ -1,0 +1,73 @@
+"""Causal grouped-query attention over the paged cache.
+
+Per hostfog/hfee internal/llm/forward.go:83-107: q/k/v projections of the normed
+input, position encoding of q and k, k and v stored in the cache at the token's
+position *before* attending, attention of every token over its own request's cache
+up to its position, output projection added to the residual stream.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict
+
+import torch
+
+from ..cache.needs import PagedKV
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.loader import TensorNeed
+from .base import Mixer, build_part, register_part
+
+
+class PagedAttention(Mixer):
+    """spec: ``width``, ``heads``, ``kv_heads``, ``head_dim``, ``position`` (a PartSpec),
+    ``window`` (None = all keys, else the last ``window`` positions), ``scale``
+    (None = head_dim**-0.5, internal/llm/forward.go:149)."""
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        q, kv = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        return {"q": TensorNeed((q, spec.width)), "k": TensorNeed((kv, spec.width)),
+                "v": TensorNeed((kv, spec.width)), "o": TensorNeed((spec.width, q))}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.heads, self.kv_heads, self.head_dim = int(spec.heads), int(spec.kv_heads), int(spec.head_dim)
+        if self.heads % self.kv_heads:
+            raise ValueError(f"heads {self.heads} must be a multiple of kv_heads {self.kv_heads}")
+        self.window = spec.get("window")
+        scale = spec.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = build_part("position", spec.position, {}, rt)
+        # one fused projection: rows [q heads | k heads | v heads]
+        self.w_qkv = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0).contiguous()
+        self.w_o = tensors["o"]
+        self.q_cols = self.heads * self.head_dim
+        self.qkv_cols = (self.heads + 2 * self.kv_heads) * self.head_dim
+
+    def cache_need(self) -> PagedKV:
+        return PagedKV(self.kv_heads, self.head_dim, self.window)
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+        n, rt = step.n, self.rt
+        cs = self.position.table(step)
+        q = rt.scratch("attn_q", (rt.max_tokens, self.q_cols))[:n]
+        if writes_cache:
+            qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n]
+            ops.linear(xn, self.w_qkv, qkv)
+            k_pool, v_pool = cache.k, cache.v
+        else:       # reads the cache another run filled: only the queries are needed
+            qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n, :self.q_cols]
+            ops.linear(xn, self.w_qkv[:self.q_cols], qkv)
+            k_pool = v_pool = None
+        ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
+                             cache.page_size, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
+                             self.position.interleaved)
+        att = rt.scratch("attn_out", (rt.max_tokens, self.q_cols))[:n]
+        ops.paged_attention(q, cache.k, cache.v, cache.block_table, cache.page_size, step.positions,
+                            step.slot_of_token, att, self.heads, self.kv_heads, self.head_dim, self.scale,
+                            int(self.window or 0), step=step)
+        ops.linear(att, self.w_o, residual, accumulate=True)
+
+
+register_part("mixer", "attention", PagedAttention)

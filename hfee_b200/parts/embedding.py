@@ -1,0 +1,56 @@
+"""Token embedding and the output head."""
+from __future__ import annotations
+
+from typing import Any, Dict
+
+import torch
+
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.loader import TensorNeed
+from .base import Part, register_part
+
+
+class TokenEmbedding(Part):
+    """``x[i,:] = table[token_i,:]``, unscaled (hostfog/hfee internal/llm/forward.go:75-77).
+    spec: ``vocab``, ``width``."""
+    category = "embedding"
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        return {"table": TensorNeed((spec.vocab, spec.width), role="table")}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.table = tensors["table"]
+
+    def forward(self, step: Any, residual: torch.Tensor) -> None:
+        ops.embed(self.table, step.token_ids, residual)
+
+
+class LinearHead(Part):
+    """``logits = x . W^T`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
+    ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121)."""
+    category = "head"
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        if spec.get("tied", False):
+            return {}
+        return {"weight": TensorNeed((spec.vocab, spec.width))}
+
+    def __init__(self, spec, tensors, rt, embedding: TokenEmbedding = None):
+        super().__init__(spec, tensors, rt)
+        if spec.get("tied", False):
+            if embedding is None:
+                raise ValueError("a tied head needs the embedding part")
+            self.weight = embedding.table
+        else:
+            self.weight = tensors["weight"]
+
+    def forward(self, xn: torch.Tensor, logits: torch.Tensor) -> None:
+        ops.linear(xn, self.weight, logits)
+
+
+register_part("embedding", "token", TokenEmbedding)
+register_part("head", "linear", LinearHead)

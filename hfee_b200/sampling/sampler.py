@@ -1,0 +1,129 @@
+"""Choosing the next token from logits.
+
+The chain of hostfog/hfee internal/llm/sampler.go:54-130: repeat penalty over the
+recent history, argmax if the temperature is <= 0, else the top-k logits in
+descending order, probabilities ``exp((l - l_max)/T)`` in float64, top-p and min-p
+cuts, and a draw ``r = U * total`` that walks the kept candidates.  The uniform
+number U comes from a counter-based generator keyed by (seed, draw index), so a
+request's draws do not depend on what else is in the batch or on preemption.
+
+Greedy and plain temperature sampling run in a device kernel over the whole batch;
+options that truncate or penalise take the same logits through the host chain.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .options import SamplingOptions
+
+_MASK = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z = (z + 0x9E3779B97F4A7C15) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def uniform(seed: int, stream: int, counter: int) -> float:
+    """Uniform in [0, 1) from (seed, stream, counter); the same function as
+    ``hfee_uniform`` in csrc/common.cuh."""
+    h = _mix64(_mix64(_mix64(seed & _MASK) ^ (stream & _MASK)) ^ (counter & _MASK))
+    return (h >> 11) * (1.0 / 9007199254740992.0)
+
+
+def fresh_seed() -> int:
+    return int.from_bytes(os.urandom(7), "little")
+
+
+def apply_repeat_penalty(logits: np.ndarray, history: Sequence[int], opts: SamplingOptions) -> None:
+    """In place, sampler.go:57-74: each distinct recent id once; positive logits are
+    divided by the penalty, the others multiplied."""
+    if not opts.penalises:
+        return
+    recent = history
+    if opts.repeat_last_n > 0 and len(recent) > opts.repeat_last_n:
+        recent = recent[len(recent) - opts.repeat_last_n:]
+    for tok in set(int(t) for t in recent):
+        if tok >= logits.shape[0]:
+            continue
+        if logits[tok] > 0:
+            logits[tok] /= np.float32(opts.repeat_penalty)
+        else:
+            logits[tok] *= np.float32(opts.repeat_penalty)
+
+
+def sample_host(logits: np.ndarray, history: Sequence[int], opts: SamplingOptions, u: float) -> int:
+    """The whole chain on the host for one row of float32 logits."""
+    logits = np.array(logits, dtype=np.float32, copy=True)
+    apply_repeat_penalty(logits, history, opts)
+    if opts.temperature <= 0:
+        return int(np.argmax(logits))               # first maximum, sampler.go:77-83
+    k = opts.top_k if 0 < opts.top_k <= logits.shape[0] else logits.shape[0]
+    if k < logits.shape[0]:
+        idx = np.argpartition(-logits, k - 1)[:k]
+        idx = idx[np.argsort(-logits[idx], kind="stable")]
+    else:
+        idx = np.argsort(-logits, kind="stable")
+    cand = logits[idx]
+    probs = np.exp(((cand - cand[0]) / np.float32(opts.temperature)).astype(np.float64))
+    probs /= probs.sum()
+    keep = len(probs)
+    if 0 < opts.top_p < 1:
+        cum = np.cumsum(probs)
+        hit = np.nonzero(cum >= float(np.float32(opts.top_p)))[0]
+        if hit.size:
+            keep = int(hit[0]) + 1
+    if opts.min_p > 0:
+        below = np.nonzero(probs[1:keep] < float(np.float32(opts.min_p)) * probs[0])[0]
+        if below.size:
+            keep = int(below[0]) + 1
+    total = float(probs[:keep].sum())
+    r = u * total
+    for i in range(keep):
+        r -= probs[i]
+        if r <= 0:
+            return int(idx[i])
+    return int(idx[keep - 1])
+
+
+class BatchSampler:
+    """Samples one token for each row of a step's logits."""
+
+    def __init__(self, device, max_rows: int):
+        self.device = torch.device(device)
+        self.max_rows = max_rows
+        pin = self.device.type == "cuda"
+        self.out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.temp = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
+        self.unif = torch.zeros(max_rows, dtype=torch.float64, device=self.device)
+        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+
+    def sample(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
+               draws: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
+        """``logits`` [m, vocab] float32 on the device; per row its options, seed, index of
+        this draw and token history (prompt + output).  Returns m token ids (host)."""
+        m = logits.shape[0]
+        assert m == len(options) <= self.max_rows
+        us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
+        if all(o.temperature <= 0 for o in options) and all(o.device_only for o in options):
+            ops.sample(logits, self.out[:m])
+        else:
+            self.temp[:m].copy_(torch.tensor([o.temperature if o.device_only else 0.0 for o in options],
+                                             dtype=torch.float32))
+            self.unif[:m].copy_(torch.tensor(us, dtype=torch.float64))
+            ops.sample(logits, self.out[:m], self.temp[:m], self.unif[:m])
+        self.out_host[:m].copy_(self.out[:m])          # device -> host, synchronises
+        tokens = [int(t) for t in self.out_host[:m]]
+        for i, o in enumerate(options):
+            if not o.device_only:
+                row = logits[i].cpu().numpy()
+                tokens[i] = sample_host(row, histories[i], o, us[i])
+        return tokens
