@@ -65,3 +65,18 @@ def test_portions_and_mixed_match_plain(tiny_dirs, cpu_ops, name):
         g = np.concatenate(got[i])
         assert g.shape[0] == len(seqs[i]) or i < 2
         assert _rel(g, refs[i][:g.shape[0]]) < 2e-5
+
+
+@pytest.mark.parametrize("scheme", ["whole", "prefill_then_decode", "portions", "mixed"])
+def test_replay_schemes_on_cpu(tiny_dirs, cpu_ops, scheme):
+    import replay_util as ru
+    cfg, w = plain.load_model_dir(tiny_dirs["B"])
+    rng = np.random.default_rng(11)
+    seqs = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (5, 17, 33, 50, 1, 40)]
+    refs = [plain.forward(cfg, w, s) for s in seqs]
+    steps = ru.mixed(seqs, live=4, seed=2) if scheme == "mixed" else getattr(ru, scheme)(seqs)
+    r = _runner(tiny_dirs["B"], page_size=16, max_tokens=9 * 16 if scheme == "mixed" else 64)
+    got = ru.run_in_process(r, steps)
+    for i in range(len(seqs)):
+        assert got[i].shape == refs[i].shape
+        assert ru.rel_err(got[i], refs[i]) < 2e-5
