@@ -1,0 +1,272 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on the Llama-3.2-1B shape with random
+bfloat16 weights, one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests whose prompts of 2,048 tokens
+are already cached (context limit 4,096).  The JSON line carries: ``value`` (decoded
+tokens a second, timed on the device over exactly K steps), ``e2e`` (the same through
+``Engine.generate``: host tokens in, host tokens out), ``prefill`` (one prompt of
+2,048 tokens), ``roofline`` (bytes a decode step must read over its time, against the
+measured HBM copy bandwidth), ``points`` (decode at batch 1 and 64), ``clocks`` and
+``gpu_launches``.  Weights (2.5 GB) and the cache of the live requests are far larger
+than the 126 MB L2, so no L2 flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama-3.2-1B shape.
+MODEL = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
+}
+FULL_LAYERS = 16
+PROMPT = 2048
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+PUBLISHED_TOK_S = 7.0      # "about 7" tokens/s for llama3.2:1b on a 2-core VPS, the reference's README
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi sampling SM clocks and throttle reasons while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.proc = None
+
+    def summary(self):
+        self.stop()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(int(parts[0]))
+                mx = max(mx, int(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    d, h, kv, hd, i, v = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                          cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    layer_params = d * (h + 2 * kv) * hd + h * hd * d + 3 * d * i
+    return {"layer_params": layer_params, "head_params": v * d,
+            "weight_bytes": 2 * (layers * layer_params + v * d) + 4 * (2 * layers + 1) * d,
+            "kv_bytes_per_token": 2 * layers * kv * hd * 2}
+
+
+def prefill_flops(cfg, layers, t):
+    n = model_numbers(cfg, layers)
+    attn = 4 * layers * cfg["num_attention_heads"] * cfg["head_dim"] * t * (t + 1) // 2
+    return 2 * t * layers * n["layer_params"] + attn + 2 * n["head_params"]
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "hostfog/hfee is a Go program with no Python package (pip: 'neither setup.py nor "
+                      "pyproject.toml found') and no Go toolchain is installed, so it cannot be built or run here"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes, if memory or time needs it")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+    from hfee_b200 import Engine, SamplingOptions, StepEntry, write_random_model
+    from hfee_b200.kernels import ops
+
+    pk = peaks()
+    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    nums = model_numbers(cfg, args.layers)
+    rng = np.random.default_rng(0)
+    tmp = tempfile.mkdtemp(prefix="hfee_bench_")
+    t0 = time.time()
+    write_random_model(tmp, cfg, seed=0, dtype="bfloat16")
+    print(f"[bench] random model written in {time.time() - t0:.0f}s", file=sys.stderr, flush=True)
+
+    max_b = 64 if not args.no_points else args.batch
+    engine = Engine(tmp, dtype="bfloat16", page_size=64, max_requests=max(max_b, args.batch), max_context=CONTEXT,
+                    max_batch_tokens=PROMPT, max_cache_tokens=max(max_b, args.batch) * CONTEXT)
+    runner = engine.runner
+    import shutil
+    shutil.rmtree(tmp, ignore_errors=True)
+    vocab = cfg["vocab_size"]
+    sample_out = torch.zeros(max(max_b, args.batch), dtype=torch.int32, device=runner.device)
+
+    def timed(fn, iters):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    # ---------------------------------------------------------------- prefill of 2,048 tokens
+    prompt = rng.integers(0, vocab, size=PROMPT).tolist()
+
+    def prefill_once(_):
+        s = runner.open()
+        runner.step([StepEntry(s, prompt, [PROMPT - 1])])
+        runner.close(s)
+
+    for _ in range(args.warmup):
+        prefill_once(0)
+    clocks = ClockSampler()
+    clocks.start()
+    p_iters = 5
+    p_ms = timed(prefill_once, p_iters) / p_iters
+    p_flops = prefill_flops(cfg, args.layers, PROMPT)
+    prefill = {"value": round(PROMPT / (p_ms / 1e3), 1), "tokens": PROMPT, "ms": round(p_ms, 3),
+               "frac": round(p_flops / (p_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode
+    def decode_point(batch, steps, warmup):
+        slots = [runner.open() for _ in range(batch)]
+        for s in slots:
+            runner.step([StepEntry(s, rng.integers(0, vocab, size=PROMPT).tolist(), [])])
+        feed = rng.integers(0, vocab, size=(warmup + steps, batch)).tolist()
+
+        def one(i):
+            logits = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            ops.sample(logits, sample_out[:batch])
+
+        for i in range(warmup):
+            one(i)
+        before = ops.launch_count()
+        ms = timed(lambda i: one(warmup + i), steps)
+        launches = ops.launch_count() - before
+        ctx = PROMPT + warmup + (steps - 1) / 2.0 + 1
+        for s in slots:
+            runner.close(s)
+        return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+                "bytes": nums["weight_bytes"] + batch * ctx * nums["kv_bytes_per_token"], "context": ctx}
+
+    main_pt = decode_point(args.batch, args.steps, args.warmup)
+    clock_summary = clocks.summary()
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_point(b, min(args.steps, 32), args.warmup)["tok_s"], 1)
+
+    # ---------------------------------------------------------------- end to end through generate()
+    e2e = None
+    if not args.no_e2e:
+        prompts = [rng.integers(0, vocab, size=PROMPT).tolist() for _ in range(args.batch)]
+        opts = SamplingOptions.greedy(num_predict=args.warmup + args.steps)
+        h0, d0 = engine.h2d_bytes, engine.d2h_bytes
+        steps_before = runner.steps_run
+        res = engine.generate(prompts, opts)
+        n_steps = max(1, runner.steps_run - steps_before)
+        eval_tokens = sum(r.stats.eval_tokens for r in res)
+        eval_s = max(r.stats.eval_seconds for r in res)
+        e2e = {"value": round(eval_tokens / eval_s, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": round((engine.h2d_bytes - h0) / n_steps, 1),
+               "d2h_bytes_per_step": round((engine.d2h_bytes - d0) / n_steps, 1)}
+
+    achieved = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape)", "value": round(main_pt["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_pt["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(main_pt["tok_s"] / PUBLISHED_TOK_S, 1), "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "llama-3.2-1b-shape", "global_batch": args.batch, "seq_len": CONTEXT,
+                   "prompt_len": PROMPT, "parallelism": "single_gpu", "layers": args.layers,
+                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_embeddings": True,
+                   "page_size": 64, "weights": "random bf16 seed 0", "l2": "inputs larger than L2",
+                   "peaks": pk["source"]},
+        "e2e": e2e,
+        "gpu_launches": int(main_pt["launches"]),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,365 @@
+// Causal grouped-query flash attention over the paged cache with bfloat16 tensor-core
+// MMAs (mma.sync.m16n8k16) and a float32 online softmax, for prefill portions,
+// single decoded tokens and mixtures of both in one launch.
+//
+// A CTA serves one (request, kv head, tile of query rows[, split of the keys]).  The
+// rows of a tile are (token, query head of the kv head's group) pairs, so the group
+// shares every key/value load.  Keys are visited in blocks of 64 positions aligned
+// to absolute multiples of 64; a block's rows are fetched page by page with
+// cp.async (double buffered), rows outside the tile's key range are zero-filled so
+// that stale page content never reaches an MMA.  With num_splits > 1 the key blocks
+// of a tile are divided among CTAs which write unnormalised partial results; the
+// combine kernel merges them in split order.
+// Reference: hostfog/hfee internal/llm/forward.go:146-178, internal/ggml/ops.go:136-150.
+#include "common.cuh"
+
+#ifndef HFEE_ATTN_EXPORT
+#define HFEE_ATTN_EXPORT 1
+#endif
+
+namespace {
+
+constexpr int BLOCK_N = 64;
+
+struct AttnParams {
+  const __nv_bfloat16* q; int ld_q;
+  __nv_bfloat16* out; int ld_o;
+  const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
+  PagedCache cache;
+  const int* cu_tokens;        // [R+1]
+  const int* slots;            // [R]
+  const int* context_before;   // [R]
+  int heads, group;            // group = heads / kv_heads
+  float scale_log2;            // scale * log2(e)
+  int window;                  // 0: all keys
+  int tokens_per_tile;         // query tokens per tile = rows / group
+  int num_splits;
+  float* part_o;               // [(token*heads + head)*num_splits + split][HD]
+  float* part_ml;              // [...][2] = (max in log2 units, sum)
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_mma_kernel(AttnParams p) {
+  constexpr int ROWS = 16 * NWARPS;
+  constexpr int PITCH = HD + 8;                 // elements; odd number of 16-byte units: conflict-free ldmatrix
+  constexpr int CHUNKS = HD / 8;                // 16-byte chunks per row
+  constexpr int THREADS = NWARPS * 32;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [ROWS][PITCH]
+  __nv_bfloat16* k_s = q_s + ROWS * PITCH;                                // [2][BLOCK_N][PITCH]
+  __nv_bfloat16* v_s = k_s + 2 * BLOCK_N * PITCH;                         // [2][BLOCK_N][PITCH]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int tile = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
+  const int kvh = blockIdx.y, r = blockIdx.z;
+
+  const int tok0 = p.cu_tokens[r], n_new = p.cu_tokens[r + 1] - tok0;
+  const int t_first = tile * p.tokens_per_tile;
+  if (t_first >= n_new) return;
+  const int t_count = min(p.tokens_per_tile, n_new - t_first);
+  const int slot = p.slots[r], before = p.context_before[r];
+  const int pos_first = before + t_first, pos_last = pos_first + t_count - 1;
+  const int key_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
+  const int rows_used = t_count * p.group;
+
+  // key blocks of this CTA
+  int b_lo = key_lo / BLOCK_N, b_hi = pos_last / BLOCK_N;
+  if (p.num_splits > 1) {
+    int per = (b_hi - b_lo + 1 + p.num_splits - 1) / p.num_splits;
+    b_lo = b_lo + split * per;
+    b_hi = min(b_hi, b_lo + per - 1);
+  }
+
+  // ---- stage Q (rows beyond rows_used are zero)
+  for (int idx = tid; idx < ROWS * CHUNKS; idx += THREADS) {
+    int row = idx / CHUNKS, ch = idx % CHUNKS;
+    bool ok = row < rows_used;
+    int t = t_first + row / p.group, hg = row % p.group;
+    const __nv_bfloat16* src = p.q + (long long)(tok0 + (ok ? t : t_first)) * p.ld_q +
+                               (long long)(kvh * p.group + (ok ? hg : 0)) * HD + ch * 8;
+    cp_async16(q_s + row * PITCH + ch * 8, src, ok);
+  }
+
+  auto load_kv = [&](int block, int stage) {
+    __nv_bfloat16* kd = k_s + stage * BLOCK_N * PITCH;
+    __nv_bfloat16* vd = v_s + stage * BLOCK_N * PITCH;
+    for (int idx = tid; idx < BLOCK_N * CHUNKS; idx += THREADS) {
+      int row = idx / CHUNKS, ch = idx % CHUNKS;
+      int pos = block * BLOCK_N + row;
+      bool ok = pos >= key_lo && pos <= pos_last;
+      long long off = ok ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
+      cp_async16(kd + row * PITCH + ch * 8, p.k_pool + off, ok);
+      cp_async16(vd + row * PITCH + ch * 8, p.v_pool + off, ok);
+    }
+  };
+
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  // positions of this thread's two rows (g and g+8 of the warp's 16)
+  int row_pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    int row = warp * 16 + g + 8 * h;
+    row_pos[h] = row < rows_used ? pos_first + row / p.group : -1;      // -1: every key masked
+  }
+
+  if (b_lo <= b_hi) load_kv(b_lo, 0);
+  cp_async_commit();
+
+  for (int b = b_lo; b <= b_hi; ++b) {
+    int stage = (b - b_lo) & 1;
+    if (b + 1 <= b_hi) load_kv(b + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const __nv_bfloat16* kt = k_s + stage * BLOCK_N * PITCH;
+    const __nv_bfloat16* vt = v_s + stage * BLOCK_N * PITCH;
+
+    // ---- S = Q K^T for this warp's 16 rows x 64 keys
+    float s[BLOCK_N / 8][4];
+#pragma unroll
+    for (int i = 0; i < BLOCK_N / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * PITCH + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < BLOCK_N / 16; ++np) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, kt + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], a, kb[0], kb[1]);
+        mma_bf16(s[2 * np + 1], a, kb[2], kb[3]);
+      }
+    }
+
+    // ---- mask, scale to log2 units, online softmax
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nt = 0; nt < BLOCK_N / 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int h = j >> 1;
+        int key = b * BLOCK_N + nt * 8 + 2 * c + (j & 1);
+        bool ok = key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
+        float v = ok ? s[nt][j] * p.scale_log2 : -INFINITY;
+        s[nt][j] = v;
+        m_new[h] = fmaxf(m_new[h], v);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
+      alpha[h] = exp2f(m_run[h] - m_use[h]);
+      m_run[h] = m_new[h];
+    }
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < BLOCK_N / 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int h = j >> 1;
+        float e = exp2f(s[nt][j] - m_use[h]);
+        s[nt][j] = e;
+        l_add[h] += e;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + l_add[h];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
+      o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
+    }
+
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + dp * 16 + (lane >> 4) * 8);
+        mma_bf16(o_acc[2 * dp], a, vb[0], vb[1]);
+        mma_bf16(o_acc[2 * dp + 1], a, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // ---- row sums across the quad, then write
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    int row = warp * 16 + g + 8 * h;
+    if (row >= rows_used) continue;
+    int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
+    if (p.num_splits == 1) {
+      float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[i][2 * h] * inv, o_acc[i][2 * h + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * c) = v;
+      }
+    } else {
+      long long idx = ((long long)(tok0 + t) * p.heads + head) * p.num_splits + split;
+      float* dst = p.part_o + idx * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
+      if (c == 0) {
+        p.part_ml[idx * 2] = m_run[h];
+        p.part_ml[idx * 2 + 1] = l_run[h];
+      }
+    }
+  }
+}
+
+// out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in order.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd,
+                                         int num_splits) {
+  int token = blockIdx.x / heads, head = blockIdx.x % heads;
+  long long base = ((long long)token * heads + head) * num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    float ms = part_ml[(base + s) * 2];
+    if (ms != -INFINITY) l += exp2f(ms - m) * part_ml[(base + s) * 2 + 1];
+  }
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      float ms = part_ml[(base + s) * 2];
+      if (ms != -INFINITY) acc += exp2f(ms - m) * part_o[(base + s) * hd + d];
+    }
+    out[(long long)token * ld_o + (long long)head * hd + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HD, int NWARPS>
+int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
+  constexpr int PITCH = HD + 8;
+  size_t smem = (size_t)(16 * NWARPS + 4 * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((unsigned)(q_tiles * p.num_splits), (unsigned)kv_heads, (unsigned)requests);
+  attention_mma_kernel<HD, NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  return hfee_check_launch("attention_mma");
+}
+
+template <int HD>
+int dispatch_warps(const AttnParams& p, int nwarps, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
+  if (nwarps == 1) return launch<HD, 1>(p, q_tiles, kv_heads, requests, stream);
+  return launch<HD, 4>(p, q_tiles, kv_heads, requests, stream);
+}
+
+}  // namespace
+
+// Scratch floats needed for `num_splits` > 1: n_tokens * heads * num_splits * (head_dim + 2).
+HFEE_API long long hfee_attention_mma_scratch_floats(int n_tokens, int heads, int head_dim, int num_splits) {
+  return num_splits > 1 ? (long long)n_tokens * heads * num_splits * (head_dim + 2) : 0;
+}
+
+// max_new: most new tokens of any request in the batch.  num_splits > 1 needs max_new * group <= rows
+// of one tile and `scratch`.  Returns HFEE_ERR_ARG for head sizes or groups it does not take.
+HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                const int* block_table, int max_pages, int page_size, const int* cu_tokens,
+                                const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
+                                int requests, int max_new, int heads, int kv_heads, int head_dim, float scale,
+                                int window, int num_splits, float* scratch, cudaStream_t stream) {
+  if (n_tokens == 0 || requests == 0) return HFEE_OK;
+  HFEE_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
+               "attention_mma: head_dim %d must be a multiple of 16 in 16..256", head_dim);
+  HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention_mma: heads %d / kv_heads %d", heads, kv_heads);
+  int group = heads / kv_heads;
+  HFEE_REQUIRE(group <= 64, "attention_mma: %d query heads per kv head exceed 64", group);
+  HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 2 == 0 && ((uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
+  HFEE_REQUIRE(requests <= 65535 && kv_heads <= 65535, "attention_mma: too many requests or kv heads for one grid");
+  HFEE_REQUIRE(max_new > 0 && num_splits >= 1, "attention_mma: bad max_new/num_splits");
+  // one warp when a single tile of 16 rows holds every request's new tokens (decode), else four
+  int nwarps = (max_new * group <= 16) ? 1 : 4;
+  int rows = 16 * nwarps;
+  int tokens_per_tile = rows / group;
+  int q_tiles = (max_new + tokens_per_tile - 1) / tokens_per_tile;
+  HFEE_REQUIRE(num_splits == 1 || (q_tiles == 1 && scratch != nullptr),
+               "attention_mma: splitting the keys needs one query tile per request and scratch memory");
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.ld_q = ld_q;
+  p.out = (__nv_bfloat16*)out; p.ld_o = ld_o;
+  p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
+  p.cache = PagedCache{block_table, max_pages, page_size, kv_heads, head_dim, (long long)kv_heads * page_size * head_dim};
+  p.cu_tokens = cu_tokens; p.slots = slots; p.context_before = context_before;
+  p.heads = heads; p.group = group;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.tokens_per_tile = tokens_per_tile; p.num_splits = num_splits;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (long long)n_tokens * heads * num_splits * head_dim : nullptr;
+  int rc;
+  switch (head_dim) {
+#define HFEE_CASE(D) case D: rc = dispatch_warps<D>(p, nwarps, q_tiles, kv_heads, requests, stream); break;
+    HFEE_CASE(16) HFEE_CASE(32) HFEE_CASE(48) HFEE_CASE(64) HFEE_CASE(80) HFEE_CASE(96) HFEE_CASE(112) HFEE_CASE(128)
+    HFEE_CASE(144) HFEE_CASE(160) HFEE_CASE(176) HFEE_CASE(192) HFEE_CASE(208) HFEE_CASE(224) HFEE_CASE(240) HFEE_CASE(256)
+#undef HFEE_CASE
+    default: return hfee_fail(HFEE_ERR_ARG, "attention_mma: head_dim %d", head_dim);
+  }
+  if (rc != HFEE_OK || num_splits == 1) return rc;
+  attention_combine_kernel<<<(unsigned)(n_tokens * heads), head_dim >= 128 ? 128 : 64, 0, stream>>>(
+      p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits);
+  return hfee_check_launch("attention_combine");
+}

@@ -179,28 +179,34 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// h[i, c] = silu(gu[i, c]) * gu[i, inter + c]; g / (1 + exp(-g)) * u in float32.
+// h[i, c] = silu(gate) * up in float32, g / (1 + exp(-g)) * u.  The fused projection's
+// columns come in groups of `granule` gate columns followed by `granule` up columns:
+// gate(c) = gu[i, (c / granule) * 2 * granule + c % granule], up(c) = gate(c) + granule
+// (granule = inter: all gate columns, then all up columns).
 // Reference: internal/ggml/ops.go:160-165.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, int ld_gu, T* __restrict__ h, int ld_h, int n, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, int ld_gu, T* __restrict__ h, int ld_h, int n, int inter,
+                              int granule) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n * inter) return;
   int i = (int)(idx / inter), c = (int)(idx % inter);
-  float g = to_f32<T>(gu[(long long)i * ld_gu + c]);
-  float u = to_f32<T>(gu[(long long)i * ld_gu + inter + c]);
+  long long gcol = (long long)(c / granule) * 2 * granule + c % granule;
+  float g = to_f32<T>(gu[(long long)i * ld_gu + gcol]);
+  float u = to_f32<T>(gu[(long long)i * ld_gu + gcol + granule]);
   h[(long long)i * ld_h + c] = from_f32<T>(g / (1.f + expf(-g)) * u);
 }
 
-HFEE_API int hfee_swiglu(const void* gu, int ld_gu, void* h, int ld_h, int n, int inter, int dtype,
+HFEE_API int hfee_swiglu(const void* gu, int ld_gu, void* h, int ld_h, int n, int inter, int granule, int dtype,
                          cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && inter > 0 && ld_gu >= 2 * inter && ld_h >= inter, "swiglu: bad sizes");
+  HFEE_REQUIRE(granule > 0 && inter % granule == 0, "swiglu: granule %d does not divide %d", granule, inter);
   long long total = (long long)n * inter;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == HFEE_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld_gu, (float*)h, ld_h, n, inter);
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld_gu, (float*)h, ld_h, n, inter, granule);
   else if (dtype == HFEE_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter);
+    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter, granule);
   else
     return hfee_fail(HFEE_ERR_ARG, "swiglu: unknown dtype %d", dtype);
   return hfee_check_launch("swiglu");

@@ -1,0 +1,182 @@
+// out[M,N] (+)= A[M,K] . W[N,K]^T for few tokens (M <= 64), bfloat16 inputs, float32
+// accumulation: the decode-step matrix product, bound by reading W once from HBM.
+//
+// A CTA owns ROWS = 8*NT consecutive weight rows and all M tokens; its warps split K
+// in interleaved blocks of 32.  Weights are the B operand of mma.sync.m16n8k16 (8
+// weight rows per tile), tokens the A operand (16 per tile), so a lane's 16-byte
+// load of a weight row feeds two MMAs directly from registers: the k order inside
+// a block is permuted identically for both operands, which leaves the dot product
+// unchanged.  Partial sums of the warps are added in warp order, so every output is
+// summed in one fixed order whatever M is.
+//
+// Epilogues: store (bf16 or f32), accumulate into a float32 output (the residual
+// add), or SwiGLU over rows interleaved as [4 gate rows | 4 up rows] per group of 8.
+// Reference: out[t*Rows+r] = Dot(W[r,:], x[t,:]), hostfog/hfee internal/ggml/ops.go:54-70
+// ("each row is read once for all n inputs").
+#include "common.cuh"
+
+namespace {
+
+constexpr int NW = 4;           // warps per CTA
+constexpr int LOADS_IN_FLIGHT = 8;   // 16-byte weight loads a lane issues before the MMAs that use them
+
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// MT: token tiles of 16; NT: weight-row tiles of 8.
+template <int MT, int NT, int EPI, typename TOut>
+__global__ void __launch_bounds__(NW * 32)
+gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
+                   long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  constexpr int ROWS = 8 * NT;
+  constexpr int UNROLL = LOADS_IN_FLIGHT / NT;     // k32-steps per batch of loads
+  __shared__ float red[NW][MT * 16][ROWS + 1];
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int g = lane >> 2, c = lane & 3;
+  int n0 = blockIdx.x * ROWS;
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+
+  const __nv_bfloat16* wrow[NT];
+  bool wok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    int r = n0 + nt * 8 + g;
+    wok[nt] = r < N;
+    wrow[nt] = W + (long long)(wok[nt] ? r : 0) * ldw;
+  }
+  const __nv_bfloat16* arow[MT][2];
+  bool aok[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int t = mt * 16 + h * 8 + g;
+      aok[mt][h] = t < M;
+      arow[mt][h] = A + (long long)(aok[mt][h] ? t : 0) * lda;
+    }
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  int steps = (K + 31) / 32;                       // k32 blocks in all
+  for (int s0 = warp; s0 < steps; s0 += NW * UNROLL) {
+    uint4 wv[UNROLL][NT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int k = (s0 + u * NW) * 32 + c * 8;
+      bool kok = (s0 + u * NW) < steps && k < K;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) wv[u][nt] = (kok && wok[nt]) ? ld_stream(wrow[nt] + k) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int k = (s0 + u * NW) * 32 + c * 8;
+      bool kok = (s0 + u * NW) < steps && k < K;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint4 lo = (kok && aok[mt][0]) ? __ldg((const uint4*)(arow[mt][0] + k)) : zero;
+        uint4 hi = (kok && aok[mt][1]) ? __ldg((const uint4*)(arow[mt][1] + k)) : zero;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, wv[u][nt].x, wv[u][nt].y);
+          mma_bf16(acc[mt][nt], lo.z, hi.z, lo.w, hi.w, wv[u][nt].z, wv[u][nt].w);
+        }
+      }
+    }
+  }
+
+  // fragment -> shared: c0,c1 = (token g, rows 2c,2c+1); c2,c3 = (token g+8, same rows)
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      red[warp][mt * 16 + g][nt * 8 + 2 * c] = acc[mt][nt][0];
+      red[warp][mt * 16 + g][nt * 8 + 2 * c + 1] = acc[mt][nt][1];
+      red[warp][mt * 16 + g + 8][nt * 8 + 2 * c] = acc[mt][nt][2];
+      red[warp][mt * 16 + g + 8][nt * 8 + 2 * c + 1] = acc[mt][nt][3];
+    }
+  __syncthreads();
+
+  if constexpr (EPI == EPI_SWIGLU) {
+    // rows of a group of 8: [gate x4 | up x4] -> 4 outputs at columns (n0/2 + group*4 ..)
+    constexpr int OUTS = ROWS / 2;
+    for (int idx = threadIdx.x; idx < MT * 16 * OUTS; idx += NW * 32) {
+      int t = idx / OUTS, o = idx % OUTS;
+      int col = n0 / 2 + o;
+      if (t >= M || col >= N / 2) continue;
+      int gr = (o / 4) * 8 + (o % 4);
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) { gate += red[w][t][gr]; up += red[w][t][gr + 4]; }
+      C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < MT * 16 * ROWS; idx += NW * 32) {
+      int t = idx / ROWS, r = idx % ROWS;
+      if (t >= M || n0 + r >= N) continue;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) v += red[w][t][r];
+      long long o = (long long)t * ldc + n0 + r;
+      if constexpr (EPI == EPI_ACCUM) C[o] = to_f32<TOut>(C[o]) + v;
+      else C[o] = from_f32<TOut>(v);
+    }
+  }
+}
+
+template <int MT, int NT>
+int launch(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
+           int epilogue, int M, int N, int K, cudaStream_t stream) {
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  unsigned grid = (unsigned)((N + 8 * NT - 1) / (8 * NT));
+#define HFEE_GO(EPI, T) gemm_stream_kernel<MT, NT, EPI, T><<<grid, NW * 32, 0, stream>>>(a, lda, w, ldw, (T*)C, ldc, M, N, K)
+  if (epilogue == EPI_ACCUM) {
+    if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
+    HFEE_GO(EPI_ACCUM, float);
+  } else if (epilogue == EPI_SWIGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
+  }
+#undef HFEE_GO
+  return hfee_check_launch("gemm_stream");
+}
+
+}  // namespace
+
+// epilogue: 0 store, 1 accumulate into float32 C, 2 SwiGLU (C is [M, N/2]; N % 8 == 0).
+HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                              int out_dtype, int epilogue, int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && M <= 64, "gemm_stream: M=%d is outside 1..64", M);
+  HFEE_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gemm_stream: K=%d must be a positive multiple of 8", K);
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
+               "gemm_stream: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
+  HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_stream: operands must be 16-byte aligned");
+  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_stream: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_stream: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_stream: ldc=%lld is too small", ldc);
+  if (M <= 16) return launch<1, 1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  if (M <= 32) return launch<2, 2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  return launch<4, 4>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+}

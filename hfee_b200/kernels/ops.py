@@ -30,7 +30,9 @@ _SIGNATURES = {
     "hfee_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "hfee_rope_table": [_P, _P, _P, _I, _I, _P],
     "hfee_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "hfee_swiglu": [_P, _I, _P, _I, _I, _I, _I, _P],
+    "hfee_swiglu": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "hfee_gemm_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -69,7 +71,22 @@ def loaded_library_path() -> Optional[str]:
     return _LIB._name if _LIB is not None else None
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (a graph replay counts its kernels)."""
+    return _LAUNCHES
+
+
+def count_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def _check(code: int, lib: ctypes.CDLL) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if code != 0:
         raise KernelLibraryError(lib.hfee_last_error().decode() or f"kernel call failed with code {code}")
 
@@ -157,13 +174,14 @@ def rope_cache_write(qkv: torch.Tensor, cs: Optional[torch.Tensor], positions: t
                                      _dt(qkv), _stream()), lib)
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[i, c] = silu(gate_up[i, c]) * gate_up[i, I + c] with I = out.shape[1]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, granule: Optional[int] = None) -> None:
+    """out[i, c] = silu(gate) * up.  Columns of ``gate_up`` come in groups of ``granule`` gate
+    columns followed by ``granule`` up columns (default: all gate columns, then all up columns)."""
     lib = library()
     n, inter = out.shape
     assert gate_up.shape[1] == 2 * inter and gate_up.dtype == out.dtype
     _check(lib.hfee_swiglu(gate_up.data_ptr(), _rows(gate_up, "gate_up"), out.data_ptr(), _rows(out, "swiglu out"),
-                           n, inter, _dt(out), _stream()), lib)
+                           n, inter, int(granule or inter), _dt(out), _stream()), lib)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -177,9 +195,50 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
                               _stream()), lib)
 
 
+STREAM_MAX_TOKENS = 64
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+
+
+def _streamable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= STREAM_MAX_TOKENS and a.shape[1] % 8 == 0
+            and _rows(a, "a") % 8 == 0 and _rows(w, "w") % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """out (+)= a @ w.T for at most 64 rows of ``a`` (bfloat16), streaming ``w`` once through
+    mma.sync tiles.  ``epilogue``: store, accumulate into float32 ``out``, or SwiGLU over rows
+    of ``w`` interleaved as [4 gate | 4 up] (then ``out`` is [m, n/2])."""
+    lib = library()
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
+    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    _check(lib.hfee_gemm_stream(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
+                                _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (+)= a @ w.T, choosing the kernel for the dtype and the shape."""
-    gemm_simt(a, w, out, accumulate)
+    if _streamable(a, w):
+        gemm_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+    else:
+        gemm_simt(a, w, out, accumulate)
+
+
+SWIGLU_GRANULE = 4
+
+
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int,
+                  scratch: torch.Tensor) -> None:
+    """out = silu(a @ w_gate^T) * (a @ w_up^T) where ``w_gate_up`` holds the rows of both in groups
+    of ``granule`` gate rows followed by ``granule`` up rows; ``scratch`` [m, 2*inner] holds the
+    projection when it is not fused."""
+    if granule == SWIGLU_GRANULE and _streamable(a, w_gate_up) and w_gate_up.shape[0] % 8 == 0:
+        gemm_stream(a, w_gate_up, out, EPI_SWIGLU)
+    else:
+        linear(a, w_gate_up, scratch)
+        swiglu(scratch, out, granule)
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
@@ -198,11 +257,57 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                                    kv_heads, head_dim, float(scale), int(window or 0), _dt(q), _stream()), lib)
 
 
+SM_COUNT = 148
+MAX_SPLITS = 32
+
+
+def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
+    """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
+    every SM about two CTAs, at least four key blocks of 64 each."""
+    want = -(-2 * SM_COUNT // max(1, requests * kv_heads))
+    return max(1, min(MAX_SPLITS, want, max_context // 256))
+
+
+def attention_mma(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, context_before, out, n_tokens,
+                  requests, max_new, heads, kv_heads, head_dim, scale, window=0, num_splits=1, scratch=None) -> None:
+    """Flash attention over the paged cache on mma.sync tensor cores (bfloat16)."""
+    lib = library()
+    for t, what in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (slots, "slots"),
+                    (context_before, "context_before")):
+        _i32(t, what)
+    assert q.dtype == k_pool.dtype == out.dtype == torch.bfloat16
+    assert k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    if num_splits > 1:
+        need = n_tokens * heads * num_splits * (head_dim + 2)
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
+    _check(lib.hfee_attention_mma(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(),
+                                  block_table.data_ptr(), block_table.shape[1], page_size, cu_tokens.data_ptr(),
+                                  slots.data_ptr(), context_before.data_ptr(), out.data_ptr(),
+                                  _rows(out, "attention out"), n_tokens, requests, max_new, heads, kv_heads,
+                                  head_dim, float(scale), int(window or 0), num_splits, _ptr(scratch), _stream()), lib)
+    if num_splits > 1:
+        count_launches(1)
+
+
 def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
-                    head_dim, scale, window=0, step=None) -> None:
-    """Attention over the cache, choosing the kernel for the dtype and the batch."""
-    attention_simt(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
-                   head_dim, scale, window)
+                    head_dim, scale, window=0, step=None, scratch=None) -> None:
+    """Attention over the cache, choosing the kernel for the dtype and the batch.  ``step`` gives
+    the per-request layout (cu_tokens, slots, context_before, max_new, max_context) that the
+    tensor-core kernel needs; without it, or in float32, the CUDA-core kernel runs."""
+    group = heads // kv_heads
+    if (step is not None and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and group <= 64 and _rows(q, "q") % 8 == 0):
+        splits = 1
+        if step.max_new * group <= 16 and scratch is not None:
+            splits = getattr(step, "attention_splits", None) or attention_splits(step.r, kv_heads, step.max_context)
+            if step.n * heads * splits * (head_dim + 2) > scratch.numel():
+                splits = 1
+        attention_mma(q, k_pool, v_pool, block_table, page_size, step.cu_tokens, step.slots, step.context_before,
+                      out, step.n, step.r, step.max_new, heads, kv_heads, head_dim, scale, window, splits, scratch)
+    else:
+        attention_simt(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
+                       head_dim, scale, window)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -44,6 +44,9 @@ class PagedAttention(Mixer):
         self.w_o = tensors["o"]
         self.q_cols = self.heads * self.head_dim
         self.qkv_cols = (self.heads + 2 * self.kv_heads) * self.head_dim
+        # partial results of a decode step whose keys are split among CTAs
+        self.split_scratch = rt.scratch("attn_partials", (rt.max_requests * self.heads * ops.MAX_SPLITS *
+                                                          (self.head_dim + 2),), torch.float32)
 
     def cache_need(self) -> PagedKV:
         return PagedKV(self.kv_heads, self.head_dim, self.window)
@@ -66,7 +69,7 @@ class PagedAttention(Mixer):
         att = rt.scratch("attn_out", (rt.max_tokens, self.q_cols))[:n]
         ops.paged_attention(q, cache.k, cache.v, cache.block_table, cache.page_size, step.positions,
                             step.slot_of_token, att, self.heads, self.kv_heads, self.head_dim, self.scale,
-                            int(self.window or 0), step=step)
+                            int(self.window or 0), step=step, scratch=self.split_scratch)
         ops.linear(att, self.w_o, residual, accumulate=True)
 
 

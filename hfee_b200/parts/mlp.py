@@ -24,16 +24,24 @@ class SwiGLUFeedForward(Part):
     def __init__(self, spec, tensors, rt):
         super().__init__(spec, tensors, rt)
         self.inner = int(spec.inner)
-        # one fused projection: rows [gate | up]
-        self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        # one fused projection.  bfloat16: rows in groups of 4 gate rows then 4 up rows, so a
+        # kernel that owns 8 consecutive rows can apply SwiGLU in its epilogue; else [gate | up].
+        gate, up = tensors["gate"], tensors["up"]
+        g = ops.SWIGLU_GRANULE
+        if gate.dtype == torch.bfloat16 and self.inner % g == 0:
+            self.granule = g
+            w = torch.stack([gate.reshape(self.inner // g, g, -1), up.reshape(self.inner // g, g, -1)], dim=1)
+            self.w_gate_up = w.reshape(2 * self.inner, -1).contiguous()
+        else:
+            self.granule = self.inner
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down"]
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any) -> None:
         n, rt = step.n, self.rt
         gu = rt.scratch("ffn_gate_up", (rt.max_tokens, 2 * self.inner))[:n]
-        ops.linear(xn, self.w_gate_up, gu)
         h = rt.scratch("ffn_hidden", (rt.max_tokens, self.inner))[:n]
-        ops.swiglu(gu, h)
+        ops.linear_swiglu(xn, self.w_gate_up, h, self.granule, gu)
         ops.linear(h, self.w_down, residual, accumulate=True)
 
 

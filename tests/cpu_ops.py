@@ -54,10 +54,17 @@ def rope_cache_write(qkv, cs, positions, slot_of_token, q_out, k_pool, v_pool, b
         v_pool[page, :, pos % page_size, :] = x[i, heads + kv_heads:].to(v_pool.dtype)
 
 
-def swiglu(gate_up, out):
+def swiglu(gate_up, out, granule=None):
     inter = out.shape[1]
-    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    granule = granule or inter
+    x = gate_up.float().reshape(gate_up.shape[0], inter // granule, 2, granule)
+    g, u = x[:, :, 0].reshape(-1, inter), x[:, :, 1].reshape(-1, inter)
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+
+
+def linear_swiglu(a, w_gate_up, out, granule, scratch):
+    linear(a, w_gate_up, scratch)
+    swiglu(scratch, out, granule)
 
 
 def linear(a, w, out, accumulate=False):
@@ -69,7 +76,7 @@ def linear(a, w, out, accumulate=False):
 
 
 def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
-                    head_dim, scale, window=0, step=None):
+                    head_dim, scale, window=0, step=None, scratch=None):
     n = q.shape[0]
     group = heads // kv_heads
     for i in range(n):
@@ -98,7 +105,8 @@ def sample(logits, out, temperature=None, uniform=None):
             out[r] = int(torch.searchsorted(cum, float(uniform[r]) * float(cum[-1])).clamp(max=logits.shape[1] - 1))
 
 
-ALL = ("embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "paged_attention", "sample")
+ALL = ("embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_swiglu",
+       "paged_attention", "sample")
 
 
 def install(monkeypatch):

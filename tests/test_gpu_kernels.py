@@ -1,0 +1,219 @@
+"""Each CUDA kernel alone against a plain float32/float64 torch reference, at sizes
+other than the engine's (odd widths, tails, head sizes from 16 to 256)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hfee_b200.kernels import ops as o
+    o.library()
+    return o
+
+
+def _close(got, ref, tol):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = float((got - ref).abs().max() / (ref.abs().max() + 1e-30))
+    assert err < tol, f"relative error {err:.3g} >= {tol}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,width,vocab", [(1, 7, 11), (33, 100, 57), (5, 2048, 300)])
+def test_embed(ops, dtype, n, width, vocab):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, width, generator=g).to(dtype).to(DEV)
+    tokens = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(n, width, dtype=torch.float32, device=DEV)
+    ops.embed(table, tokens, out)
+    assert torch.equal(out, table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,width,eps", [(1, 1, 1e-5), (3, 97, 1e-6), (17, 2048, 1e-5), (4, 5000, 1e-3)])
+def test_rmsnorm(ops, out_dtype, n, width, eps):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(n + 2, width, generator=g) * 3).to(DEV)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DEV)
+    rows = torch.tensor([(i * 2 + 1) % (n + 2) for i in range(n)], dtype=torch.int32, device=DEV)
+    for idx in (None, rows):
+        out = torch.empty(n, width, dtype=out_dtype, device=DEV)
+        ops.rmsnorm(x, w, out, eps, rows=idx)
+        src = (x[:n] if idx is None else x[idx.long()]).double()
+        ref = src / torch.sqrt((src * src).mean(1, keepdim=True) + eps) * w.double()
+        _close(out, ref, 1e-5 if out_dtype == torch.float32 else 6e-3)
+    out = torch.empty(n, width, dtype=torch.float32, device=DEV)
+    ops.rmsnorm(x, w, out, eps, add_unit=True)
+    src = x[:n].double()
+    _close(out, src / torch.sqrt((src * src).mean(1, keepdim=True) + eps) * (1 + w.double()), 1e-5)
+
+
+def test_rope_table_far_positions(ops):
+    """float64 angles: a position of 100000 keeps cos/sin right to float32 rounding."""
+    pos = torch.tensor([0, 1, 63, 64, 4097, 100000, 131071], dtype=torch.int32, device=DEV)
+    inv = torch.tensor([1.0 / (500000.0 ** (2 * i / 64)) for i in range(32)], dtype=torch.float64, device=DEV)
+    out = torch.empty(len(pos), 32, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(pos, inv, out)
+    ang = pos.double()[:, None] * inv[None, :]
+    assert float((out[..., 0].double() - ang.cos()).abs().max()) < 1e-7
+    assert float((out[..., 1].double() - ang.sin()).abs().max()) < 1e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,hd,rope_dim,inter", [(4, 2, 16, 16, False), (3, 1, 32, 32, True),
+                                                         (2, 2, 48, 16, False), (5, 5, 64, 32, True)])
+def test_rope_cache_write(ops, dtype, heads, kv, hd, rope_dim, inter):
+    g = torch.Generator().manual_seed(2)
+    n, page, max_pages, slots = 23, 16, 4, 3
+    qkv = torch.randn(n, (heads + 2 * kv) * hd, generator=g).to(dtype).to(DEV)
+    slot = torch.randint(0, slots, (n,), generator=g, dtype=torch.int32)
+    pos = torch.zeros(n, dtype=torch.int32)
+    seen = {}
+    for i in range(n):                       # distinct (slot, position) pairs
+        s = int(slot[i]); seen[s] = seen.get(s, 5) + 1; pos[i] = seen[s] * 2
+    table = torch.randperm(slots * max_pages, generator=g).reshape(slots, max_pages).to(torch.int32).to(DEV)
+    kp = torch.zeros(slots * max_pages, kv, page, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(n, heads * hd, dtype=dtype, device=DEV)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * i / rope_dim)) for i in range(rope_dim // 2)], dtype=torch.float64, device=DEV)
+    cs = torch.empty(n, rope_dim // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(pos.to(DEV), inv, cs)
+    ops.rope_cache_write(qkv, cs, pos.to(DEV), slot.to(DEV), q, kp, vp, table, page, heads, kv, hd, rope_dim, inter)
+
+    x = qkv.double().cpu().reshape(n, heads + 2 * kv, hd)
+    ang = pos.double()[:, None] * inv.cpu()[None, :]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    rot = x[:, :heads + kv].clone()
+    half = rope_dim // 2
+    if inter:
+        a, b = x[:, :heads + kv, 0:rope_dim:2], x[:, :heads + kv, 1:rope_dim:2]
+        rot[..., 0:rope_dim:2], rot[..., 1:rope_dim:2] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[:, :heads + kv, :half], x[:, :heads + kv, half:rope_dim]
+        rot[..., :half], rot[..., half:rope_dim] = a * c - b * s, a * s + b * c
+    tol = 1e-6 if dtype == torch.float32 else 6e-3
+    _close(q, rot[:, :heads].reshape(n, -1), tol)
+    for i in range(n):
+        pg = int(table[int(slot[i]), int(pos[i]) // page])
+        _close(kp[pg, :, int(pos[i]) % page], rot[i, heads:], tol)
+        assert torch.equal(vp[pg, :, int(pos[i]) % page].cpu().double(), x[i, heads + kv:])
+    written = sum(1 for _ in range(n))
+    assert int((kp.float().abs().sum(-1) > 0).sum()) == written * kv       # nothing else was touched
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,inter,granule", [(3, 172, None), (7, 172, 4), (2, 8192, 4), (1, 5, None)])
+def test_swiglu(ops, dtype, n, inter, granule):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(n, 2 * inter, generator=g) * 2).to(dtype).to(DEV)
+    out = torch.empty(n, inter, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out, granule)
+    gr = granule or inter
+    x = gu.double().reshape(n, inter // gr, 2, gr)
+    gate, up = x[:, :, 0].reshape(n, inter), x[:, :, 1].reshape(n, inter)
+    _close(out, gate / (1 + torch.exp(-gate)) * up, 1e-6 if dtype == torch.float32 else 6e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 7, 3), (64, 64, 16), (65, 130, 100), (33, 256, 172), (200, 96, 513)])
+def test_gemm_simt(ops, dtype, m, n, k):
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(m, k, generator=g).to(dtype).to(DEV)
+    w = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    ref = a.double() @ w.double().t()
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemm_simt(a, w, out)
+    _close(out, ref, 1e-5)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_simt(a, w, acc, accumulate=True)
+    _close(acc, base.double() + ref, 1e-5)
+    if dtype == torch.bfloat16:
+        outb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_simt(a, w, outb)
+        _close(outb, ref, 6e-3)
+
+
+def test_gemm_simt_rows_do_not_depend_on_batch(ops):
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(70, 333, generator=g).to(DEV)
+    w = torch.randn(129, 333, generator=g).to(DEV)
+    full = torch.empty(70, 129, device=DEV)
+    ops.gemm_simt(a, w, full)
+    one = torch.empty(1, 129, device=DEV)
+    ops.gemm_simt(a[41:42], w, one)
+    assert torch.equal(one[0], full[41])
+
+
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(8, 8), (24, 40), (100, 96), (2048, 2048), (257, 1000)])
+def test_gemm_stream(ops, m, n, k):
+    g = torch.Generator().manual_seed(6)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    ref = a.double() @ w.double().t()
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemm_stream(a, w, out)
+    _close(out, ref, 1e-5)
+    outb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_stream(a, w, outb)
+    _close(outb, ref, 6e-3)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_stream(a, w, acc, ops.EPI_ACCUM)
+    _close(acc, base.double() + ref, 1e-5)
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("inner,k", [(4, 8), (172, 64), (1000, 96), (8192, 256)])
+def test_gemm_stream_swiglu(ops, m, inner, k):
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inner, k, generator=g) * 0.2).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([gate.reshape(inner // 4, 4, k), up.reshape(inner // 4, 4, k)], 1).reshape(2 * inner, k).contiguous().to(DEV)
+    out = torch.empty(m, inner, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty(m, 2 * inner, dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a, w, out, 4, scratch)
+    gd, ud = a.double().cpu() @ gate.double().t(), a.double().cpu() @ up.double().t()
+    _close(out, gd / (1 + torch.exp(-gd)) * ud, 6e-3)
+
+
+def test_gemm_stream_refuses_unaligned(ops):
+    from hfee_b200.kernels import KernelLibraryError
+    a = torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelLibraryError, match="multiple of 8"):
+        ops.gemm_stream(a, w, torch.empty(2, 8, dtype=torch.float32, device=DEV))
+    # the dispatcher falls back to the CUDA-core kernel instead
+    out = torch.empty(2, 8, dtype=torch.float32, device=DEV)
+    ops.linear(a, w, out)
+    assert float(out.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("m,v", [(1, 5), (3, 257), (4, 128256), (2, 1000)])
+def test_sample_greedy_and_temperature(ops, m, v):
+    g = torch.Generator().manual_seed(8)
+    logits = torch.randn(m, v, generator=g).to(DEV)
+    logits[0, v // 2] = logits[0, v - 1] = 9.0          # a tie: the first maximum wins
+    out = torch.zeros(m, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    assert out.tolist() == [int(torch.argmax(logits[i].cpu())) for i in range(m)]
+    assert out[0] == v // 2
+    temp = torch.full((m,), 0.7, dtype=torch.float32, device=DEV)
+    for u in (0.0, 0.25, 0.5, 0.999999):
+        un = torch.full((m,), u, dtype=torch.float64, device=DEV)
+        ops.sample(logits, out, temp, un)
+        for i in range(m):
+            p = torch.exp((logits[i].double().cpu() - logits[i].double().max().cpu()) / 0.7)
+            cum = torch.cumsum(p, 0)
+            want = int(torch.searchsorted(cum, u * float(cum[-1])).clamp(max=v - 1))
+            got = int(out[i])
+            # equal up to rounding of the running sum at the boundary
+            assert got == want or abs(float(cum[got] - cum[want])) / float(cum[-1]) < 1e-9

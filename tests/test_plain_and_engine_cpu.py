@@ -80,3 +80,17 @@ def test_replay_schemes_on_cpu(tiny_dirs, cpu_ops, scheme):
     for i in range(len(seqs)):
         assert got[i].shape == refs[i].shape
         assert ru.rel_err(got[i], refs[i]) < 2e-5
+
+
+def test_bfloat16_weight_layouts_on_cpu(tiny_dirs, cpu_ops):
+    """bfloat16 mode fuses and interleaves projection rows at load; the result must not change."""
+    cfg, w = plain.load_model_dir(tiny_dirs["A"], round_to_bf16=True)
+    rng = np.random.default_rng(1)
+    toks = rng.integers(0, cfg.vocab, size=21).tolist()
+    ref = plain.forward(cfg, w, toks)
+    e = EngineConfig(dtype="bfloat16", page_size=16, max_requests=2, max_context=64, max_cache_tokens=64,
+                     max_batch_tokens=64, device="cpu")
+    r = ModelRunner(tiny_dirs["A"], e)
+    out = r.step([StepEntry(r.open(), toks, list(range(len(toks))))]).numpy()
+    assert r.model.blocks[0].feed_forward.granule == 4
+    assert float(np.max(np.abs(out - ref)) / np.max(np.abs(ref))) < 2e-2
