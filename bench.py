@@ -139,6 +139,9 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="profiling aid: run just one of the measurements (the JSON line is then partial)")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -161,14 +164,18 @@ def main():
     write_random_model(tmp, cfg, seed=0, dtype="bfloat16")
     print(f"[bench] random model written in {time.time() - t0:.0f}s", file=sys.stderr, flush=True)
 
+    if args.only != "all":
+        args.no_points = args.no_e2e = True
     max_b = 64 if not args.no_points else args.batch
     engine = Engine(tmp, dtype="bfloat16", page_size=64, max_requests=max(max_b, args.batch), max_context=CONTEXT,
-                    max_batch_tokens=PROMPT, max_cache_tokens=max(max_b, args.batch) * CONTEXT)
+                    max_batch_tokens=PROMPT, max_cache_tokens=max(max_b, args.batch) * CONTEXT,
+                    use_cuda_graphs=not args.no_graphs)
     runner = engine.runner
     import shutil
     shutil.rmtree(tmp, ignore_errors=True)
     vocab = cfg["vocab_size"]
     sample_out = torch.zeros(max(max_b, args.batch), dtype=torch.int32, device=runner.device)
+    argmax_scratch = engine.sampler.argmax_scratch
 
     def timed(fn, iters):
         torch.cuda.synchronize()
@@ -188,15 +195,23 @@ def main():
         runner.step([StepEntry(s, prompt, [PROMPT - 1])])
         runner.close(s)
 
-    for _ in range(args.warmup):
-        prefill_once(0)
     clocks = ClockSampler()
-    clocks.start()
-    p_iters = 5
-    p_ms = timed(prefill_once, p_iters) / p_iters
-    p_flops = prefill_flops(cfg, args.layers, PROMPT)
-    prefill = {"value": round(PROMPT / (p_ms / 1e3), 1), "tokens": PROMPT, "ms": round(p_ms, 3),
-               "frac": round(p_flops / (p_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    prefill = None
+    if args.only in ("all", "prefill"):
+        for _ in range(args.warmup):
+            prefill_once(0)
+        clocks.start()
+        p_iters = 5 if args.only == "all" else 1
+        print(f"[bench] timed prefill starts after {ops.launch_count()} launches", file=sys.stderr, flush=True)
+        p_ms = timed(prefill_once, p_iters) / p_iters
+        p_flops = prefill_flops(cfg, args.layers, PROMPT)
+        prefill = {"value": round(PROMPT / (p_ms / 1e3), 1), "tokens": PROMPT, "ms": round(p_ms, 3),
+                   "frac": round(p_flops / (p_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    else:
+        clocks.start()
+    if args.only == "prefill":
+        print(json.dumps({"prefill": prefill, "clocks": clocks.summary()}))
+        return 0
 
     # ---------------------------------------------------------------- decode
     def decode_point(batch, steps, warmup):
@@ -207,11 +222,12 @@ def main():
 
         def one(i):
             logits = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
-            ops.sample(logits, sample_out[:batch])
+            ops.argmax(logits, sample_out[:batch], argmax_scratch)
 
         for i in range(warmup):
             one(i)
         before = ops.launch_count()
+        print(f"[bench] timed decode (batch {batch}) starts after {before} launches", file=sys.stderr, flush=True)
         ms = timed(lambda i: one(warmup + i), steps)
         launches = ops.launch_count() - before
         ctx = PROMPT + warmup + (steps - 1) / 2.0 + 1

@@ -67,10 +67,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD, int NWARPS>
+// KSPLIT = false: each warp owns 16 query rows and visits all 64 keys of a block (prefill).
+// KSPLIT = true: the tile has 16 rows; each warp visits 16 of a block's 64 keys with a softmax
+// state of its own, and the warps' results are merged at the end (decode: few rows, many keys).
+template <int HD, int NWARPS, bool KSPLIT>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_mma_kernel(AttnParams p) {
-  constexpr int ROWS = 16 * NWARPS;
+  static_assert(!KSPLIT || NWARPS * 16 == BLOCK_N, "key-split mode needs 16 keys per warp");
+  constexpr int ROWS = KSPLIT ? 16 : 16 * NWARPS;
+  constexpr int WKEYS = KSPLIT ? 16 : BLOCK_N;        // keys of a block one warp visits
   constexpr int PITCH = HD + 8;                 // elements; odd number of 16-byte units: conflict-free ldmatrix
   constexpr int CHUNKS = HD / 8;                // 16-byte chunks per row
   constexpr int THREADS = NWARPS * 32;
@@ -81,6 +86,8 @@ attention_mma_kernel(AttnParams p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
+  const int wrow = KSPLIT ? 0 : warp * 16;            // first tile row of this warp
+  const int wkey = KSPLIT ? warp * 16 : 0;            // first key (within a block) of this warp
   const int tile = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
   const int kvh = blockIdx.y, r = blockIdx.z;
 
@@ -135,7 +142,7 @@ attention_mma_kernel(AttnParams p) {
   int row_pos[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    int row = warp * 16 + g + 8 * h;
+    int row = wrow + g + 8 * h;
     row_pos[h] = row < rows_used ? pos_first + row / p.group : -1;      // -1: every key masked
   }
 
@@ -153,19 +160,19 @@ attention_mma_kernel(AttnParams p) {
     const __nv_bfloat16* vt = v_s + stage * BLOCK_N * PITCH;
 
     // ---- S = Q K^T for this warp's 16 rows x 64 keys
-    float s[BLOCK_N / 8][4];
+    float s[WKEYS / 8][4];
 #pragma unroll
-    for (int i = 0; i < BLOCK_N / 8; ++i)
+    for (int i = 0; i < WKEYS / 8; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
       uint32_t a[4];
-      ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * PITCH + ks * 16 + (lane >> 4) * 8);
+      ldmatrix_x4(a, q_s + (wrow + (lane & 15)) * PITCH + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-      for (int np = 0; np < BLOCK_N / 16; ++np) {
+      for (int np = 0; np < WKEYS / 16; ++np) {
         uint32_t kb[4];
-        ldmatrix_x4(kb, kt + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+        ldmatrix_x4(kb, kt + (wkey + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], a, kb[0], kb[1]);
         mma_bf16(s[2 * np + 1], a, kb[2], kb[3]);
       }
@@ -174,11 +181,11 @@ attention_mma_kernel(AttnParams p) {
     // ---- mask, scale to log2 units, online softmax
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-    for (int nt = 0; nt < BLOCK_N / 8; ++nt)
+    for (int nt = 0; nt < WKEYS / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         int h = j >> 1;
-        int key = b * BLOCK_N + nt * 8 + 2 * c + (j & 1);
+        int key = b * BLOCK_N + wkey + nt * 8 + 2 * c + (j & 1);
         bool ok = key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
         float v = ok ? s[nt][j] * p.scale_log2 : -INFINITY;
         s[nt][j] = v;
@@ -195,7 +202,7 @@ attention_mma_kernel(AttnParams p) {
     }
     float l_add[2] = {0.f, 0.f};
 #pragma unroll
-    for (int nt = 0; nt < BLOCK_N / 8; ++nt)
+    for (int nt = 0; nt < WKEYS / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         int h = j >> 1;
@@ -213,7 +220,7 @@ attention_mma_kernel(AttnParams p) {
 
     // ---- O += P V
 #pragma unroll
-    for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+    for (int kk = 0; kk < WKEYS / 16; ++kk) {
       uint32_t a[4];
       a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
       a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -222,7 +229,7 @@ attention_mma_kernel(AttnParams p) {
 #pragma unroll
       for (int dp = 0; dp < HD / 16; ++dp) {
         uint32_t vb[4];
-        ldmatrix_x4_trans(vb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + dp * 16 + (lane >> 4) * 8);
+        ldmatrix_x4_trans(vb, vt + (wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + dp * 16 + (lane >> 4) * 8);
         mma_bf16(o_acc[2 * dp], a, vb[0], vb[1]);
         mma_bf16(o_acc[2 * dp + 1], a, vb[2], vb[3]);
       }
@@ -231,15 +238,57 @@ attention_mma_kernel(AttnParams p) {
   }
   cp_async_wait<0>();
 
-  // ---- row sums across the quad, then write
+  // ---- row sums across the quad
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
+
+  if constexpr (KSPLIT) {
+    // merge the warps' (max, sum, O) per row in warp order; the K/V stages are free now
+    float* mo = reinterpret_cast<float*>(k_s);                 // [NWARPS][16][HD]
+    float* mm = mo + NWARPS * 16 * HD;                         // [NWARPS][16] max
+    float* ml = mm + NWARPS * 16;                              // [NWARPS][16] sum
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int row = g + 8 * h;
+      float* dst = mo + (warp * 16 + row) * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
+      if (c == 0) { mm[warp * 16 + row] = m_run[h]; ml[warp * 16 + row] = l_run[h]; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_used * (HD / 2); idx += THREADS) {
+      int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, mm[w * 16 + row]);
+      float l = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) {
+        float mw = mm[w * 16 + row];
+        float sc = mw == -INFINITY ? 0.f : exp2f(mw - m);
+        l += sc * ml[w * 16 + row];
+        o0 += sc * mo[(w * 16 + row) * HD + d];
+        o1 += sc * mo[(w * 16 + row) * HD + d + 1];
+      }
+      int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
+      if (p.num_splits == 1) {
+        float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
+        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+      } else {
+        long long pi = ((long long)(tok0 + t) * p.heads + head) * p.num_splits + split;
+        *reinterpret_cast<float2*>(p.part_o + pi * HD + d) = make_float2(o0, o1);
+        if (d == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
+      }
+    }
+  } else {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    int row = warp * 16 + g + 8 * h;
+    int row = wrow + g + 8 * h;
     if (row >= rows_used) continue;
     int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
     if (p.num_splits == 1) {
@@ -261,6 +310,7 @@ attention_mma_kernel(AttnParams p) {
         p.part_ml[idx * 2 + 1] = l_run[h];
       }
     }
+  }
   }
 }
 
@@ -288,25 +338,28 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
-template <int HD, int NWARPS>
+template <int HD, bool KSPLIT>
 int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
+  constexpr int NWARPS = 4;
   constexpr int PITCH = HD + 8;
-  size_t smem = (size_t)(16 * NWARPS + 4 * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
+  constexpr int ROWS = KSPLIT ? 16 : 64;
+  size_t smem = (size_t)(ROWS + 4 * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS, KSPLIT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid((unsigned)(q_tiles * p.num_splits), (unsigned)kv_heads, (unsigned)requests);
-  attention_mma_kernel<HD, NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  attention_mma_kernel<HD, NWARPS, KSPLIT><<<grid, NWARPS * 32, smem, stream>>>(p);
   return hfee_check_launch("attention_mma");
 }
 
 template <int HD>
-int dispatch_warps(const AttnParams& p, int nwarps, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
-  if (nwarps == 1) return launch<HD, 1>(p, q_tiles, kv_heads, requests, stream);
-  return launch<HD, 4>(p, q_tiles, kv_heads, requests, stream);
+int dispatch_mode(const AttnParams& p, bool ksplit, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
+  if (ksplit) return launch<HD, true>(p, q_tiles, kv_heads, requests, stream);
+  return launch<HD, false>(p, q_tiles, kv_heads, requests, stream);
 }
 
 }  // namespace
@@ -332,9 +385,9 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 2 == 0 && ((uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
   HFEE_REQUIRE(requests <= 65535 && kv_heads <= 65535, "attention_mma: too many requests or kv heads for one grid");
   HFEE_REQUIRE(max_new > 0 && num_splits >= 1, "attention_mma: bad max_new/num_splits");
-  // one warp when a single tile of 16 rows holds every request's new tokens (decode), else four
-  int nwarps = (max_new * group <= 16) ? 1 : 4;
-  int rows = 16 * nwarps;
+  // when 16 rows hold every request's new tokens (decode) the warps split the keys instead
+  bool ksplit = max_new * group <= 16;
+  int rows = ksplit ? 16 : 64;
   int tokens_per_tile = rows / group;
   int q_tiles = (max_new + tokens_per_tile - 1) / tokens_per_tile;
   HFEE_REQUIRE(num_splits == 1 || (q_tiles == 1 && scratch != nullptr),
@@ -352,7 +405,7 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   p.part_ml = scratch ? scratch + (long long)n_tokens * heads * num_splits * head_dim : nullptr;
   int rc;
   switch (head_dim) {
-#define HFEE_CASE(D) case D: rc = dispatch_warps<D>(p, nwarps, q_tiles, kv_heads, requests, stream); break;
+#define HFEE_CASE(D) case D: rc = dispatch_mode<D>(p, ksplit, q_tiles, kv_heads, requests, stream); break;
     HFEE_CASE(16) HFEE_CASE(32) HFEE_CASE(48) HFEE_CASE(64) HFEE_CASE(80) HFEE_CASE(96) HFEE_CASE(112) HFEE_CASE(128)
     HFEE_CASE(144) HFEE_CASE(160) HFEE_CASE(176) HFEE_CASE(192) HFEE_CASE(208) HFEE_CASE(224) HFEE_CASE(240) HFEE_CASE(256)
 #undef HFEE_CASE

@@ -113,13 +113,14 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, int ld_qkv, const f
   int i = blockIdx.x;
   int hd = cache.head_dim, kvh = cache.kv_heads;
   int half = rope_dim / 2;
+  int per_block = (int)blockDim.x * gridDim.y;    // work items are spread over the blocks of grid.y
   int pos = positions[i];
   int slot = slot_of_token[i];
   const T* row = qkv + (long long)i * ld_qkv;
   int total_heads = k_pool ? heads + 2 * kvh : heads;   // q only when this run reads another run's cache
   // one work item = (head, pair index within the head); hd/2 items per head
   int per_head = hd / 2;
-  for (int w = threadIdx.x; w < total_heads * per_head; w += blockDim.x) {
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total_heads * per_head; w += per_block) {
     int h = w / per_head, p = w % per_head;
     const T* src = row + (long long)h * hd;
     int a, b;
@@ -166,11 +167,14 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
   PagedCache c{block_table, max_pages, page_size, kv_heads, head_dim,
                (long long)kv_heads * page_size * head_dim};
   int threads = 256;
+  int items = (heads + 2 * kv_heads) * (head_dim / 2);
+  dim3 grid((unsigned)n, (unsigned)((items + threads - 1) / threads));
+  if (grid.y > 64) grid.y = 64;
   if (dtype == HFEE_F32)
-    rope_cache_kernel<float><<<n, threads, 0, stream>>>((const float*)qkv, ld_qkv, (const float2*)cs, positions,
+    rope_cache_kernel<float><<<grid, threads, 0, stream>>>((const float*)qkv, ld_qkv, (const float2*)cs, positions,
         slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c, heads, rope_dim, interleaved);
   else if (dtype == HFEE_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
+    rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
         positions, slot_of_token, (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, c,
         heads, rope_dim, interleaved);
   else

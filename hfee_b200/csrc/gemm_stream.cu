@@ -17,8 +17,7 @@
 
 namespace {
 
-constexpr int NW = 4;           // warps per CTA
-constexpr int LOADS_IN_FLIGHT = 8;   // 16-byte weight loads a lane issues before the MMAs that use them
+constexpr int LOADS_IN_FLIGHT = 4;   // 16-byte weight loads per lane in one batch; two batches are in flight
 
 enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
@@ -37,9 +36,10 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return v;
 }
 
-// MT: token tiles of 16; NT: weight-row tiles of 8.
-template <int MT, int NT, int EPI, typename TOut>
-__global__ void __launch_bounds__(NW * 32)
+// MT: token tiles of 16; NT: weight-row tiles of 8; NW: warps per CTA (they split K, so the
+// fewer tokens there are, the more warps keep loads in flight).
+template <int MT, int NT, int NW, int EPI, typename TOut>
+__global__ void __launch_bounds__(NW * 32, 2048 / (NW * 32) >= 4 ? 2 : 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
                    long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
   constexpr int ROWS = 8 * NT;
@@ -77,16 +77,19 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
     }
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  int steps = (K + 31) / 32;                       // k32 blocks in all
-  for (int s0 = warp; s0 < steps; s0 += NW * UNROLL) {
-    uint4 wv[UNROLL][NT];
+  const int steps = (K + 31) / 32;                       // k32 blocks in all; warp w takes w, w+NW, ...
+  uint4 wv[2][UNROLL][NT];
+
+  auto load_batch = [&](int s0, uint4 (&dst)[UNROLL][NT]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       int k = (s0 + u * NW) * 32 + c * 8;
       bool kok = (s0 + u * NW) < steps && k < K;
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) wv[u][nt] = (kok && wok[nt]) ? ld_stream(wrow[nt] + k) : zero;
+      for (int nt = 0; nt < NT; ++nt) dst[u][nt] = (kok && wok[nt]) ? ld_stream(wrow[nt] + k) : zero;
     }
+  };
+  auto compute_batch = [&](int s0, const uint4 (&src)[UNROLL][NT]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       int k = (s0 + u * NW) * 32 + c * 8;
@@ -97,10 +100,22 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
         uint4 hi = (kok && aok[mt][1]) ? __ldg((const uint4*)(arow[mt][1] + k)) : zero;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, wv[u][nt].x, wv[u][nt].y);
-          mma_bf16(acc[mt][nt], lo.z, hi.z, lo.w, hi.w, wv[u][nt].z, wv[u][nt].w);
+          mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, src[u][nt].x, src[u][nt].y);
+          mma_bf16(acc[mt][nt], lo.z, hi.z, lo.w, hi.w, src[u][nt].z, src[u][nt].w);
         }
       }
+    }
+  };
+
+  // two batches of weight loads are kept in flight: the next one is issued before this one is used
+  constexpr int STRIDE = NW * UNROLL;
+  load_batch(warp, wv[0]);
+  for (int s0 = warp; s0 < steps; s0 += 2 * STRIDE) {
+    load_batch(s0 + STRIDE, wv[1]);
+    compute_batch(s0, wv[0]);
+    if (s0 + STRIDE < steps) {
+      load_batch(s0 + 2 * STRIDE, wv[0]);
+      compute_batch(s0 + STRIDE, wv[1]);
     }
   }
 
@@ -143,13 +158,13 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
   }
 }
 
-template <int MT, int NT>
+template <int MT, int NT, int NW>
 int launch(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
            int epilogue, int M, int N, int K, cudaStream_t stream) {
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   unsigned grid = (unsigned)((N + 8 * NT - 1) / (8 * NT));
-#define HFEE_GO(EPI, T) gemm_stream_kernel<MT, NT, EPI, T><<<grid, NW * 32, 0, stream>>>(a, lda, w, ldw, (T*)C, ldc, M, N, K)
+#define HFEE_GO(EPI, T) gemm_stream_kernel<MT, NT, NW, EPI, T><<<grid, NW * 32, 0, stream>>>(a, lda, w, ldw, (T*)C, ldc, M, N, K)
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
     HFEE_GO(EPI_ACCUM, float);
@@ -176,7 +191,7 @@ HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long 
   HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_stream: unknown epilogue %d", epilogue);
   HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_stream: SwiGLU needs N %% 8 == 0, got %d", N);
   HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_stream: ldc=%lld is too small", ldc);
-  if (M <= 16) return launch<1, 1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
-  if (M <= 32) return launch<2, 2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
-  return launch<4, 4>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  if (M <= 16) return launch<1, 1, 16>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  if (M <= 32) return launch<2, 2, 8>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  return launch<4, 4, 4>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
 }

@@ -77,7 +77,69 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   }
 }
 
+// Greedy choice for many rows at once: each row's columns are divided among `chunks` blocks
+// (stage 1), then one block per row picks among the chunk winners (stage 2).  Ties go to the
+// lower index in both stages, so the result is the first maximum.
+__global__ void __launch_bounds__(THREADS)
+argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int chunks, float* __restrict__ part) {
+  __shared__ float s_val[THREADS];
+  __shared__ int s_idx[THREADS];
+  int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (long long)r * ld;
+  int per = (V + chunks - 1) / chunks;
+  int begin = min(V, ch * per), end = min(V, begin + per);
+  float best = -INFINITY;
+  int best_i = V;
+  for (int c = begin + tid; c < end; c += THREADS) {
+    float v = row[c];
+    if (best_i == V || v > best) { best = v; best_i = c; }      // ascending c: the first maximum stays
+  }
+  s_val[tid] = best;
+  s_idx[tid] = best_i;
+  __syncthreads();
+  for (int o = THREADS / 2; o > 0; o >>= 1) {
+    if (tid < o) {
+      float v2 = s_val[tid + o];
+      int i2 = s_idx[tid + o];
+      if (i2 < V && (s_idx[tid] == V || v2 > s_val[tid] || (v2 == s_val[tid] && i2 < s_idx[tid]))) {
+        s_val[tid] = v2;
+        s_idx[tid] = i2;
+      }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    part[((long long)r * chunks + ch) * 2] = s_val[0];
+    part[((long long)r * chunks + ch) * 2 + 1] = __int_as_float(s_idx[0]);
+  }
+}
+
+__global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out) {
+  int r = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  float best = -INFINITY;
+  int best_i = V;
+  for (int ch = 0; ch < chunks; ++ch) {
+    float v = part[((long long)r * chunks + ch) * 2];
+    int i = __float_as_int(part[((long long)r * chunks + ch) * 2 + 1]);
+    if (i < V && (best_i == V || v > best)) { best = v; best_i = i; }   // chunks ascend: ties keep the first
+  }
+  out[r] = best_i;
+}
+
 }  // namespace
+
+// scratch: M * chunks * 2 floats.
+HFEE_API int hfee_argmax(const float* logits, long long ld, int M, int V, int chunks, float* scratch, int* out,
+                         cudaStream_t stream) {
+  if (M == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && V > 0 && ld >= V && chunks > 0 && chunks <= 1024 && scratch != nullptr,
+               "argmax: bad sizes M=%d V=%d chunks=%d", M, V, chunks);
+  HFEE_REQUIRE(M <= 65535, "argmax: too many rows");
+  argmax_stage1_kernel<<<dim3((unsigned)chunks, (unsigned)M), THREADS, 0, stream>>>(logits, ld, V, chunks, scratch);
+  argmax_stage2_kernel<<<M, 32, 0, stream>>>(scratch, V, chunks, out);
+  return hfee_check_launch("argmax");
+}
 
 HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const float* temperature,
                          const double* uniform, int* out, cudaStream_t stream) {

@@ -106,6 +106,7 @@ class Step:
         self.cu_tokens, self.slots = d[o:o + r + 1], d[o + r + 1:o + 2 * r + 1]
         self.context_before, self.context_after = d[o + 2 * r + 1:o + 3 * r + 1], d[o + 3 * r + 1:o + 4 * r + 1]
         self.max_context = max((s + k for _, s, k in self.requests), default=0)
+        self.planning_context = self.max_context      # what launch heuristics (key splits) plan for
         self.max_new = max((k for _, _, k in self.requests), default=0)
         self.decode_only = all(k == 1 for _, _, k in self.requests)
         self.logits_capacity = max(buffers.max_requests, 1 << max(0, (m - 1)).bit_length())

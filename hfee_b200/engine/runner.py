@@ -39,6 +39,11 @@ class ModelRunner:
         self.buffers = StepBuffers(e.max_batch_tokens, e.max_requests, self.device)
         self.vocab = self.spec.vocab
         self.steps_run = 0
+        # decode-only steps are captured in a CUDA graph per batch size: first sight runs
+        # eagerly (and makes every scratch buffer), second sight captures, later ones replay
+        self._graphs = {}
+        self._graph_seen = set()
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ requests
     def open(self) -> int:
@@ -80,9 +85,38 @@ class ModelRunner:
             cache.reserve(e.slot, cache.length[e.slot] + len(e.tokens))
         cache.sync()
         step = Step(entries, cache.length, self.buffers)
-        logits = self.model.forward(step, cache.views())
+        if (self.engine.use_cuda_graphs and self.device.type == "cuda" and step.decode_only
+                and all(tuple(e.want) == (0,) for e in entries)):
+            logits = self._graphed_forward(step)
+        else:
+            logits = self.model.forward(step, cache.views())
         for e in entries:
             cache.commit(e.slot, cache.length[e.slot] + len(e.tokens))
         self.steps_run += 1
         self.last_step = step
         return logits
+
+    def _graphed_forward(self, step: Step) -> torch.Tensor:
+        """A decode-only step through a CUDA graph keyed by its batch size.  The step's integers
+        live at the same device addresses for every step of that size and are copied in before the
+        replay, block tables likewise; launch parameters that depend on context lengths are planned
+        for the longest context the engine allows."""
+        from ..kernels import ops
+        key = step.r
+        step.planning_context = self.cache.max_context
+        hit = self._graphs.get(key)
+        if hit is None:
+            if key not in self._graph_seen:
+                self._graph_seen.add(key)
+                return self.model.forward(step, self.cache.views())
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(step, self.cache.views())
+            hit = self._graphs[key] = (graph, out, ops.launch_count() - before)
+        graph, out, kernels = hit
+        graph.replay()
+        ops.count_launches(kernels)
+        self.graph_replays += 1
+        return out

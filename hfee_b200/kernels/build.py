@@ -90,6 +90,14 @@ def _compile_one(nvcc: str, src: str, obj: str) -> None:
     _say(f"compiled {src} ({time.time() - t0:.0f}s)")
 
 
+def _prune(root: str, keep: str) -> None:
+    """Remove builds of older source versions (folders named by another digest)."""
+    for name in os.listdir(root):
+        path = os.path.join(root, name)
+        if name != keep and os.path.isdir(path) and len(name) == 16:
+            shutil.rmtree(path, ignore_errors=True)
+
+
 def build(force: bool = False) -> str:
     """Build the library if it is not there yet; returns its path."""
     out = library_path()
@@ -124,6 +132,7 @@ def build(force: bool = False) -> str:
                 raise KernelBuildError(f"link failed:\n{' '.join(cmd)}\n{proc.stdout}")
             os.replace(tmp, out)
             _say(f"built {LIB_NAME} in {time.time() - t0:.0f}s")
+            _prune(os.path.dirname(out_dir), keep=os.path.basename(out_dir))
             return out
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

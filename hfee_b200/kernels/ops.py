@@ -36,6 +36,7 @@ _SIGNATURES = {
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P],
 }
 
 
@@ -263,9 +264,9 @@ MAX_SPLITS = 32
 
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
     """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
-    every SM about two CTAs, at least four key blocks of 64 each."""
-    want = -(-2 * SM_COUNT // max(1, requests * kv_heads))
-    return max(1, min(MAX_SPLITS, want, max_context // 256))
+    every SM about four CTAs, at least two key blocks of 64 each."""
+    want = -(-4 * SM_COUNT // max(1, requests * kv_heads))
+    return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 
 def attention_mma(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, context_before, out, n_tokens,
@@ -300,7 +301,8 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
             and group <= 64 and _rows(q, "q") % 8 == 0):
         splits = 1
         if step.max_new * group <= 16 and scratch is not None:
-            splits = getattr(step, "attention_splits", None) or attention_splits(step.r, kv_heads, step.max_context)
+            splits = getattr(step, "attention_splits", None) or attention_splits(
+                step.r, kv_heads, getattr(step, "planning_context", step.max_context))
             if step.n * heads * splits * (head_dim + 2) > scratch.numel():
                 splits = 1
         attention_mma(q, k_pool, v_pool, block_table, page_size, step.cu_tokens, step.slots, step.context_before,
@@ -321,3 +323,17 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
         assert temperature.dtype == torch.float32 and uniform.dtype == torch.float64
     _check(lib.hfee_sample(logits.data_ptr(), _rows(logits, "logits"), m, v, _ptr(temperature), _ptr(uniform),
                            out.data_ptr(), _stream()), lib)
+
+
+ARGMAX_CHUNKS = 64
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of logits[r]; ``scratch`` holds rows * ARGMAX_CHUNKS * 2 floats."""
+    lib = library()
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and scratch.dtype == torch.float32
+    m, v = logits.shape
+    assert scratch.numel() >= m * ARGMAX_CHUNKS * 2
+    _check(lib.hfee_argmax(logits.data_ptr(), _rows(logits, "logits"), m, v, ARGMAX_CHUNKS, scratch.data_ptr(),
+                           out.data_ptr(), _stream()), lib)
+    count_launches(1)

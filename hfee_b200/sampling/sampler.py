@@ -105,6 +105,7 @@ class BatchSampler:
         self.temp = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
         self.unif = torch.zeros(max_rows, dtype=torch.float64, device=self.device)
         self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self.argmax_scratch = torch.zeros(max_rows * ops.ARGMAX_CHUNKS * 2, dtype=torch.float32, device=self.device)
 
     def sample(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
                draws: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
@@ -114,7 +115,7 @@ class BatchSampler:
         assert m == len(options) <= self.max_rows
         us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
         if all(o.temperature <= 0 for o in options) and all(o.device_only for o in options):
-            ops.sample(logits, self.out[:m])
+            ops.argmax(logits, self.out[:m], self.argmax_scratch)
         else:
             self.temp[:m].copy_(torch.tensor([o.temperature if o.device_only else 0.0 for o in options],
                                              dtype=torch.float32))

@@ -206,6 +206,9 @@ def test_sample_greedy_and_temperature(ops, m, v):
     ops.sample(logits, out)
     assert out.tolist() == [int(torch.argmax(logits[i].cpu())) for i in range(m)]
     assert out[0] == v // 2
+    out2 = torch.full((m,), -1, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out2, torch.empty(m * ops.ARGMAX_CHUNKS * 2, dtype=torch.float32, device=DEV))
+    assert torch.equal(out, out2)
     temp = torch.full((m,), 0.7, dtype=torch.float32, device=DEV)
     for u in (0.0, 0.25, 0.5, 0.999999):
         un = torch.full((m,), u, dtype=torch.float64, device=DEV)

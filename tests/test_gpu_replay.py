@@ -71,3 +71,38 @@ def test_trace_run_binary(tiny_dirs, refs, tmp_path, dtype):
     got = ru.run_trace_binary(tiny_dirs["B"], dtype, steps, str(tmp_path / "out"), max_tokens=384,
                               vocab=cfg.vocab)
     check(got, seqs, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_through_cuda_graphs(tiny_dirs, refs, dtype):
+    """Three requests decoded token by token for 150 steps across many pages, with the
+    decode steps captured in and replayed from CUDA graphs; one request ends early so the
+    batch size (and the graph) changes."""
+    import plain_llama as plain
+    from hfee_b200 import EngineConfig, ModelRunner, StepEntry
+    cfg, w = plain.load_model_dir(tiny_dirs["B"], round_to_bf16=(dtype == "bfloat16"))
+    seqs = sequences(cfg.vocab, (160, 151, 90), seed=21)
+    ref = [plain.forward(cfg, w, s) for s in seqs]
+    e = EngineConfig(dtype=dtype, page_size=16, max_requests=4, max_context=256, max_cache_tokens=27 * 16,
+                     max_batch_tokens=64, use_cuda_graphs=True)
+    runner = ModelRunner(tiny_dirs["B"], e)
+    slots = [runner.open() for _ in seqs]
+    heads = [10, 1, 5]
+    runner.step([StepEntry(s, q[:h], []) for s, q, h in zip(slots, seqs, heads)])
+    at = list(heads)
+    got = [[] for _ in seqs]
+    live = [0, 1, 2]
+    while live:
+        entries = [StepEntry(slots[i], [seqs[i][at[i]]], [0]) for i in live]
+        rows = runner.step(entries).float().cpu().numpy()
+        for j, i in enumerate(live):
+            got[i].append(rows[j].copy())
+            at[i] += 1
+        for i in list(live):
+            if at[i] == len(seqs[i]):
+                runner.close(slots[i])
+                live.remove(i)
+    assert runner.graph_replays > 100
+    for i in range(3):
+        err = ru.rel_err(np.stack(got[i]), ref[i][heads[i]:])
+        assert err < TOL[dtype], f"request {i}: relative error {err:.3g}"
