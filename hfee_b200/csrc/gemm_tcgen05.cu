@@ -1,0 +1,345 @@
+// out[M,N] (+)= A[M,K] . W[N,K]^T on the 5th-generation tensor cores: bfloat16 operands
+// staged in shared memory by TMA (128-byte swizzle, no multicast), tcgen05.mma issued by
+// one thread with the float32 accumulator in tensor memory, tcgen05.ld for the epilogue.
+//
+// One CTA computes a 128 x BN tile (BN = 128 or 256) with K in blocks of 64:
+//   warp 0     TMA producer   waits empty[s], arms full[s] with the stage's bytes, issues 2 loads
+//   warp 1     MMA issuer     allocates TMEM; waits full[s], issues 4 MMAs (K = 16 each),
+//                             commits to empty[s]; after the last block commits to tmem_full
+//   warps 2-5  epilogue       wait tmem_full, read their 32 accumulator lanes, write C
+// Tiles at the edges rely on TMA's zero fill for loads and on predicates for stores; K may
+// be any multiple of 8 (16-byte row pitch), its tail is zero-filled too.
+//
+// Every mbarrier wait is bounded: a wait that runs out sets an abort flag that ends all
+// other waits of the CTA, records a code in `status` and lets the CTA free its tensor
+// memory and return.
+// Reference: out[t*Rows+r] = Dot(W[r,:], x[t,:]), hostfog/hfee internal/ggml/ops.go:54-70.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 4u << 20;     // polls (with back-off sleeps) before a wait gives up: ~ a second
+
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Waits for the phase with `parity` to complete; false if the wait ran out or the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) {
+      __nanosleep(i > 4096 ? 256 : 32);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) in the
+// 128-byte swizzle: 8-row groups 1024 bytes apart (stride offset), leading offset 1 (unused
+// for swizzled K-major), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct TileCfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int W_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;      // + slack to align the base to 1024
+};
+
+template <int BN, int EPI, typename TOut>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        int s = kb % STAGES;
+        uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u, &abort_flag)) break;
+        unsigned char* a_dst = tiles + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, kb * BK, m0, &full_bar[s]);
+        tma_load_2d(a_dst + Cfg::A_BYTES, &map_w, kb * BK, n0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        int s = kb % STAGES;
+        uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
+        ok = mbar_wait(&full_bar[s], phase, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t a_addr = smem_u32(tiles + s * Cfg::STAGE_BYTES);
+        uint64_t da = make_desc(a_addr), dw = make_desc(a_addr + Cfg::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)       // 16 bf16 = 32 bytes further along K: +2 in 16-byte units
+          tc_mma(tmem_base, da + 2 * k, dw + 2 * k, idesc, (kb | k) != 0);
+        tc_commit(&empty_bar[s]);
+      }
+      tc_commit(&tmem_full_bar);
+    }
+  } else {
+    // epilogue warp w reads TMEM lanes 32*(w%4) .. +31 = tile rows of the same numbers
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    bool ok = mbar_wait(&tmem_full_bar, 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t v[32];
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 32), v);
+        tc_wait_ld();
+        const int col0 = n0 + ch * 32;
+        if (row >= M || col0 >= N) continue;
+        if constexpr (EPI == EPI_SWIGLU) {
+          // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col/2
+          TOut* dst = C + (long long)row * ldc + col0 / 2;
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (col0 + gq * 8 + i + 4 >= N) continue;
+              float gate = __uint_as_float(v[gq * 8 + i]), up = __uint_as_float(v[gq * 8 + 4 + i]);
+              dst[gq * 4 + i] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+            }
+        } else {
+          TOut* dst = C + (long long)row * ldc + col0;
+          const bool full = col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0;
+          if (full) {
+            if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                       __uint_as_float(v[j + 3]));
+                if constexpr (EPI == EPI_ACCUM) {
+                  float4 c = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(dst) + j);
+                  o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                }
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + j) = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j >= N) continue;
+              float o = __uint_as_float(v[j]);
+              if constexpr (EPI == EPI_ACCUM) o += to_f32<TOut>(dst[j]);
+              dst[j] = from_f32<TOut>(o);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // loads that were issued may still be landing in this CTA's shared memory: give them time
+    for (int i = 0; i < 400; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row pitch `ld` elements; box = 64 x box_rows.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return HFEE_OK;
+}
+
+template <int BN, int EPI, typename TOut>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
+           cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));     // M tiles fastest: a W tile is shared in L2
+  gemm_tc_kernel<BN, EPI, TOut><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(ma, mw, (TOut*)C, ldc, M, N, K, status);
+  return hfee_check_launch("gemm_tcgen05");
+}
+
+template <int BN>
+int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int out_dtype, int epilogue, int M,
+             int N, int K, int* status, cudaStream_t stream) {
+  if (epilogue == EPI_ACCUM) {
+    if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: accumulate needs a float32 output");
+    return launch<BN, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, stream);
+  }
+  if (epilogue == EPI_SWIGLU) {
+    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue writes bfloat16");
+    return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+  }
+  if (out_dtype == HFEE_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+  return launch<BN, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
+}
+
+}  // namespace
+
+// A, W: bfloat16, 16-byte aligned, leading dimensions multiples of 8.  epilogue: 0 store, 1 accumulate
+// into float32 C, 2 SwiGLU over W rows interleaved [4 gate | 4 up] (C is [M, N/2] bfloat16).
+// `status` (device int, may be null) is set to 1 if a CTA gave up waiting.  block_n: 128 or 256.
+HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                               int out_dtype, int epilogue, int M, int N, int K, int block_n, int* status,
+                               cudaStream_t stream) {
+  if (M == 0 || N == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "gemm_tcgen05: K=%d must be a positive multiple of 8", K);
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
+               "gemm_tcgen05: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
+  HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
+  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_tcgen05: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_tcgen05: ldc=%lld is too small", ldc);
+  HFEE_REQUIRE(block_n == 128 || block_n == 256, "gemm_tcgen05: block_n must be 128 or 256");
+  HFEE_REQUIRE((M + BM - 1) / BM <= 2147483647 && (N + block_n - 1) / block_n <= 65535, "gemm_tcgen05: grid too large");
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc != HFEE_OK) return rc;
+  rc = make_map(&mw, W, N, K, ldw, block_n);
+  if (rc != HFEE_OK) return rc;
+  if (block_n == 256) return dispatch<256>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, stream);
+  return dispatch<128>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, stream);
+}

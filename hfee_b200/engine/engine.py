@@ -13,6 +13,7 @@ from typing import Any, Callable, Dict, List, Optional, Sequence, Union
 import torch
 
 from ..config import EngineConfig
+from ..kernels import ops
 from ..sampling import BatchSampler, SamplingOptions
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -109,6 +110,7 @@ class Engine:
                         on_token(i, r.output[emitted[i]])
                         emitted[i] += 1
             sched.pop_finished()
+        ops.check_status()
         return [GenerationResult(list(r.output), self.decode(r.output), r.stats) for r in requests]
 
     def run_step(self, sched: Scheduler) -> int:

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "hfee_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "hfee_swiglu": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -197,6 +198,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
 
 
 STREAM_MAX_TOKENS = 64
+USE_TCGEN05 = True
+SM_COUNT = 148
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
 
 
@@ -219,10 +222,52 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                                 _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
 
 
+_STATUS: Optional[torch.Tensor] = None
+
+
+def _status() -> torch.Tensor:
+    global _STATUS
+    if _STATUS is None:
+        _STATUS = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _STATUS
+
+
+def check_status() -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
+    if _STATUS is not None and int(_STATUS.item()) != 0:
+        _STATUS.zero_()
+        raise KernelLibraryError("a tensor-core GEMM gave up waiting on a barrier; its output is invalid")
+
+
+def _tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and _rows(a, "a") % 8 == 0
+            and _rows(w, "w") % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE,
+                 block_n: Optional[int] = None) -> None:
+    """out (+)= a @ w.T with tcgen05.mma tiles of 128 x block_n fed by TMA (bfloat16 in, float32
+    accumulation in tensor memory).  Epilogues as in :func:`gemm_stream`."""
+    lib = library()
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
+    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    if block_n is None:
+        # wide tiles halve shared-memory traffic per flop; narrow ones fill the SMs when there are few tiles
+        tiles_256 = -(-m // 128) * -(-n // 256)
+        block_n = 256 if tiles_256 >= SM_COUNT else 128
+    _check(lib.hfee_gemm_tcgen05(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
+                                 _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, block_n,
+                                 _status().data_ptr(), _stream()), lib)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (+)= a @ w.T, choosing the kernel for the dtype and the shape."""
     if _streamable(a, w):
         gemm_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+    elif USE_TCGEN05 and _tensor_core_ok(a, w):
+        gemm_tcgen05(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     else:
         gemm_simt(a, w, out, accumulate)
 
@@ -235,8 +280,11 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, g
     """out = silu(a @ w_gate^T) * (a @ w_up^T) where ``w_gate_up`` holds the rows of both in groups
     of ``granule`` gate rows followed by ``granule`` up rows; ``scratch`` [m, 2*inner] holds the
     projection when it is not fused."""
-    if granule == SWIGLU_GRANULE and _streamable(a, w_gate_up) and w_gate_up.shape[0] % 8 == 0:
+    fusable = granule == SWIGLU_GRANULE and w_gate_up.shape[0] % 8 == 0
+    if fusable and _streamable(a, w_gate_up):
         gemm_stream(a, w_gate_up, out, EPI_SWIGLU)
+    elif fusable and USE_TCGEN05 and _tensor_core_ok(a, w_gate_up) and out.dtype == torch.bfloat16:
+        gemm_tcgen05(a, w_gate_up, out, EPI_SWIGLU)
     else:
         linear(a, w_gate_up, scratch)
         swiglu(scratch, out, granule)
@@ -258,7 +306,6 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                                    kv_heads, head_dim, float(scale), int(window or 0), _dt(q), _stream()), lib)
 
 
-SM_COUNT = 148
 MAX_SPLITS = 32
 
 

@@ -1,0 +1,73 @@
+"""The tcgen05/TMA GEMM alone against a float64 reference: full tiles, ragged edges in
+every dimension, K tails, both tile widths and every epilogue."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _err(got, ref):
+    return float((got.double().cpu() - ref).abs().max() / (ref.abs().max() + 1e-30))
+
+
+def _f32_tol(k):
+    """Float32 accumulation in the tensor core rounds the running sum once per MMA (K = 16), and
+    it truncates, so errors add up instead of averaging out: K/16 steps of one float32 ulp
+    (2^-23 of the running sum) each, plus the rounding of the stored result."""
+    return 2e-6 + (k / 16) * 2.0 ** -23
+
+
+SHAPES = [(128, 128, 64), (128, 256, 128), (256, 128, 512), (65, 8, 8), (200, 300, 96), (129, 257, 72),
+          (1000, 96, 2048), (2048, 3072, 2048), (333, 1000, 8192)]
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_store_and_accumulate(m, n, k, block_n):
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    ref = a.double().cpu() @ w.double().cpu().t()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(a, w, out, ops.EPI_STORE, block_n)
+    ops.check_status()
+    assert _err(out, ref) < _f32_tol(k)
+    outb = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(a, w, outb, ops.EPI_STORE, block_n)
+    assert _err(outb, ref) < 6e-3
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_tcgen05(a, w, acc, ops.EPI_ACCUM, block_n)
+    ops.check_status()
+    assert _err(acc, base.double().cpu() + ref) < _f32_tol(k)
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (300, 172, 96), (2048, 8192, 2048), (70, 1000, 264)])
+def test_swiglu_epilogue(m, inner, k, block_n):
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(inner)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    w = torch.stack([gate.reshape(inner // 4, 4, k), up.reshape(inner // 4, 4, k)], 1).reshape(2 * inner, k).contiguous().to(DEV)
+    out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(a, w, out, ops.EPI_SWIGLU, block_n)
+    ops.check_status()
+    gd, ud = a.double().cpu() @ gate.double().t(), a.double().cpu() @ up.double().t()
+    assert _err(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
+
+
+def test_strided_operands():
+    """Views with a leading dimension larger than K (a slice of a wider buffer)."""
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(5)
+    big_a = torch.randn(150, 256, generator=g).to(torch.bfloat16).to(DEV)
+    big_w = torch.randn(90, 512, generator=g).to(torch.bfloat16).to(DEV)
+    a, w = big_a[:, :128], big_w[:, 256:384]
+    out = torch.empty(150, 90, dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(a, w, out)
+    ops.check_status()
+    assert _err(out, a.double().cpu() @ w.double().cpu().t()) < _f32_tol(128)
