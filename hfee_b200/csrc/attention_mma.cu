@@ -416,3 +416,59 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
       p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits);
   return hfee_check_launch("attention_combine");
 }
+
+// ------------------------------------------------------------------------------------------
+// The same split-key attention for callers that cannot allocate: its partial results go to a
+// fixed array in this library instead of caller-provided scratch.  See no_alloc.h.
+#include "no_alloc.h"
+
+namespace {
+
+// Partial (max, sum, output) cells of one call.  A host-side name only stands in for this array;
+// the kernels get its device address, looked up once per device below.
+static __device__ __align__(256) float g_noalloc_scratch[HFEE_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+// Device address of the array on the current device (set-up on the first call per device).
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+    return hfee_fail(HFEE_ERR_ARG, "attention_decode_noalloc: device ordinal %d is outside 0..%d", dev, NOALLOC_MAX_DEVICES - 1);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return hfee_fail(HFEE_ERR_CUDA, "attention_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return HFEE_OK;
+}
+
+}  // namespace
+
+HFEE_API int hfee_attention_decode_noalloc(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                           const int* block_table, int max_pages, int page_size,
+                                           const int* cu_tokens, const int* slots, const int* context_before,
+                                           void* out, int ld_o, int n_tokens, int requests, int max_new, int heads,
+                                           int kv_heads, int head_dim, float scale, int window, int num_splits,
+                                           cudaStream_t stream) {
+  if (n_tokens == 0 || requests == 0) return HFEE_OK;
+  HFEE_REQUIRE(num_splits >= 2, "attention_decode_noalloc: num_splits=%d; this entry point is the split-key variant (>= 2)", num_splits);
+  HFEE_REQUIRE(n_tokens > 0 && heads > 0 && head_dim > 0, "attention_decode_noalloc: bad sizes");
+  long long need = (long long)n_tokens * heads * num_splits * (head_dim + 2);
+  HFEE_REQUIRE(need <= (long long)HFEE_NOALLOC_SCRATCH_FLOATS,
+               "attention_decode_noalloc: %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of partial "
+               "results exceed the built-in scratch of %d floats; use fewer splits or hfee_attention_mma with "
+               "scratch of your own", n_tokens, heads, num_splits, head_dim, need, (int)HFEE_NOALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc != HFEE_OK) return rc;
+  return hfee_attention_mma(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots,
+                            context_before, out, ld_o, n_tokens, requests, max_new, heads, kv_heads, head_dim, scale,
+                            window, num_splits, scratch, stream);
+}
