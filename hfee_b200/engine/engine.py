@@ -17,7 +17,7 @@ from ..kernels import ops
 from ..sampling import BatchSampler, SamplingOptions
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import Request, RequestStats, Scheduler
+from .scheduler import FinishReason, Request, RequestStats, Scheduler
 
 
 @dataclass
@@ -102,8 +102,16 @@ class Engine:
             sched.add(req)
             requests.append(req)
         emitted = [0] * len(requests)
+        cut = {}                     # request index -> text cut at its stop string
         while not sched.idle:
             self.run_step(sched)
+            for i, r in enumerate(requests):       # stop strings (text.go:41-78), when text is available
+                if r.options.stop and self.tokenizer is not None and not r.finished and r.output:
+                    text = self.decode(r.output)
+                    hits = [text.find(s) for s in r.options.stop if s and s in text]
+                    if hits:
+                        cut[i] = text[:min(hits)]
+                        sched.finish(r, FinishReason.STOP)
             if on_token is not None:
                 for i, r in enumerate(requests):
                     while emitted[i] < len(r.output):
@@ -111,7 +119,8 @@ class Engine:
                         emitted[i] += 1
             sched.pop_finished()
         ops.check_status()
-        return [GenerationResult(list(r.output), self.decode(r.output), r.stats) for r in requests]
+        return [GenerationResult(list(r.output), cut.get(i, self.decode(r.output)), r.stats)
+                for i, r in enumerate(requests)]
 
     def run_step(self, sched: Scheduler) -> int:
         """Plan, run and account for one step; returns the number of tokens it ran."""

@@ -109,6 +109,11 @@ class Scheduler:
             request.finished = request.stats.done_reason = FinishReason.ABORT
             self._done.append(request)
 
+    def finish(self, request: Request, reason: str) -> None:
+        """End a running request from outside (a stop string matched, say)."""
+        if not request.finished:
+            self._finish(request, reason)
+
     @property
     def idle(self) -> bool:
         return not self.waiting and not self.running
