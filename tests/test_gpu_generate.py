@@ -1,0 +1,134 @@
+"""Generation through the Python entry point: greedy tokens equal the plain implementation's,
+seeded sampling does not depend on the batch, preemption under a tiny cache changes nothing."""
+import numpy as np
+import pytest
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(cfg, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg.vocab, size=n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("name,lengths,steps", [("A", (5, 17, 33), 16), ("B", (1, 9, 40, 100), 24)])
+def test_greedy_generation_float32_equals_plain(tiny_dirs, name, lengths, steps):
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs[name])
+    prompts = prompts_for(cfg, lengths, seed=3)
+    want = [plain.greedy_generate(cfg, w, p, steps) for p in prompts]
+    eng = Engine(tiny_dirs[name], dtype="float32", page_size=16, max_requests=4, max_context=128,
+                 max_batch_tokens=64, prefill_chunk=16)
+    res = eng.generate(prompts, SamplingOptions.greedy(num_predict=steps))
+    assert [r.token_ids for r in res] == want
+    for r, p in zip(res, prompts):
+        assert r.stats.prompt_tokens == len(p) and r.stats.eval_tokens == steps and r.stats.done_reason == "length"
+        assert r.stats.eval_seconds > 0 and r.text is None
+
+
+def test_greedy_generation_bfloat16_follows_plain_where_the_margin_allows(tiny_dirs):
+    """bfloat16 may flip a near-tie; wherever the plain top-1 margin exceeds the tolerance the
+    engine must pick the same token (teacher-forced along the plain continuation)."""
+    from hfee_b200 import EngineConfig, ModelRunner, StepEntry
+    cfg, w = plain.load_model_dir(tiny_dirs["B"], round_to_bf16=True)
+    prompt = prompts_for(cfg, (40,), seed=5)[0]
+    cont = plain.greedy_generate(cfg, w, prompt, 24)
+    seq = prompt + cont
+    ref = plain.forward(cfg, w, seq)
+    runner = ModelRunner(tiny_dirs["B"], EngineConfig(dtype="bfloat16", page_size=16, max_requests=2, max_context=128,
+                                                      max_batch_tokens=64))
+    s = runner.open()
+    got = [runner.step([StepEntry(s, seq[:40], [39])]).float().cpu().numpy()[0].copy()]
+    for t in range(40, len(seq) - 1):
+        got.append(runner.step([StepEntry(s, [seq[t]], [0])]).float().cpu().numpy()[0].copy())
+    checked = 0
+    for row, r in zip(got, ref[39:]):
+        top = np.sort(r)[::-1]
+        if top[0] - top[1] > 2 * 2e-2 * np.abs(r).max():
+            assert int(np.argmax(row)) == int(np.argmax(r))
+            checked += 1
+    assert checked >= 5
+
+
+def test_first_tokens_of_a_sequence(tiny_dirs):
+    """Positions 0, 1, 2 one by one (a one-token prompt, then single tokens) in both dtypes."""
+    from hfee_b200 import EngineConfig, ModelRunner, StepEntry
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 2e-2)):
+        cfg, w = plain.load_model_dir(tiny_dirs["A"], round_to_bf16=(dtype == "bfloat16"))
+        seq = [7, 200, 31, 0]
+        ref = plain.forward(cfg, w, seq)
+        runner = ModelRunner(tiny_dirs["A"], EngineConfig(dtype=dtype, page_size=16, max_requests=2, max_context=64,
+                                                          max_batch_tokens=16, use_cuda_graphs=False))
+        s = runner.open()
+        for t, tok in enumerate(seq):
+            row = runner.step([StepEntry(s, [tok], [0])]).float().cpu().numpy()[0]
+            assert np.abs(row - ref[t]).max() / np.abs(ref[t]).max() < tol, (dtype, t)
+
+
+def test_preemption_under_a_tiny_cache_changes_no_token(tiny_dirs):
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs["A"])
+    prompts = prompts_for(cfg, (20, 25, 30), seed=8)
+    want = [plain.greedy_generate(cfg, w, p, 20) for p in prompts]
+    eng = Engine(tiny_dirs["A"], dtype="float32", page_size=16, max_requests=3, max_context=128,
+                 max_batch_tokens=64, max_cache_tokens=7 * 16)        # 7 pages: not enough for all three to finish
+    sched_holder = {}
+    orig = eng.new_scheduler
+
+    def spy():
+        sched_holder["s"] = orig()
+        return sched_holder["s"]
+
+    eng.new_scheduler = spy
+    res = eng.generate(prompts, SamplingOptions.greedy(num_predict=20))
+    assert sched_holder["s"].preemptions > 0
+    assert [r.token_ids for r in res] == want
+    assert eng.runner.cache.free_pages() == 7 and eng.runner.cache.free_slots() == 3
+
+
+def test_seeded_sampling_does_not_depend_on_the_batch(tiny_dirs):
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, _ = plain.load_model_dir(tiny_dirs["A"])
+    prompts = prompts_for(cfg, (6, 11, 19), seed=4)
+    eng = Engine(tiny_dirs["A"], dtype="float32", page_size=16, max_requests=4, max_context=128, max_batch_tokens=64)
+    plain_t = SamplingOptions(temperature=0.9, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=11, num_predict=12)
+    chain = SamplingOptions(temperature=0.9, seed=11, num_predict=12)          # top-k 40, top-p 0.9, penalty 1.1
+    for opts in (plain_t, chain):
+        together = [r.token_ids for r in eng.generate(prompts, opts)]
+        alone = [eng.generate([p], opts)[0].token_ids for p in prompts]
+        assert together == alone
+        assert together != [r.token_ids for r in eng.generate(prompts, opts.with_(seed=12))]
+    greedy = [r.token_ids for r in eng.generate(prompts, SamplingOptions.greedy(12))]
+    assert greedy != together
+
+
+def test_eos_stops_generation_without_emitting_it(tiny_dirs, tmp_path):
+    import json, os, shutil
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs["A"])
+    prompt = prompts_for(cfg, (9,), seed=2)[0]
+    cont = plain.greedy_generate(cfg, w, prompt, 10)
+    d = str(tmp_path / "m")
+    shutil.copytree(tiny_dirs["A"], d)
+    c = json.load(open(os.path.join(d, "config.json")))
+    c["eos_token_id"] = cont[4]
+    json.dump(c, open(os.path.join(d, "config.json"), "w"))
+    eng = Engine(d, dtype="float32", page_size=16, max_requests=2, max_context=64, max_batch_tokens=32)
+    r = eng.generate([prompt], SamplingOptions.greedy())[0]
+    first = cont.index(cont[4])
+    assert r.token_ids == cont[:first] and r.stats.done_reason == "stop"
+
+
+def test_cli_run_with_prompt_ids(tiny_dirs):
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w = plain.load_model_dir(tiny_dirs["A"])
+    want = plain.greedy_generate(cfg, w, [5, 6, 7], 6)
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "hfee-b200"), "run", tiny_dirs["A"], "--prompt-ids",
+                        "5,6,7", "--temperature", "0", "--repeat-penalty", "1", "--num-predict", "6", "--dtype",
+                        "float32", "--num-ctx", "256", "--verbose"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    assert p.stdout.split("\n")[0].split() == [str(t) for t in want]
+    assert "eval count:           6 token(s)" in p.stdout and "prompt eval count:    3 token(s)" in p.stdout

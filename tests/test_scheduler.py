@@ -137,7 +137,8 @@ def test_admission_waits_for_the_first_portions_pages():
     run_plan(cache, s, plan)
     assert [e.request.id for e in s.plan()] == ["a"] and list(s.waiting) == [b]
     c = req("c", 8)
-    s.waiting.appendleft(c)                            # a shorter one at the head of the queue fits
+    s.add(c)
+    s.waiting.rotate(1)                                # a shorter one at the head of the queue fits
     plan = s.plan()
     assert [(e.request.id, len(e.tokens)) for e in plan] == [("a", 1), ("c", 8)] and list(s.waiting) == [b]
 
