@@ -73,6 +73,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int NWARPS, bool KSPLIT>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_mma_kernel(AttnParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   static_assert(!KSPLIT || NWARPS * 16 == BLOCK_N, "key-split mode needs 16 keys per warp");
   constexpr int ROWS = KSPLIT ? 16 : 16 * NWARPS;
   constexpr int WKEYS = KSPLIT ? 16 : BLOCK_N;        // keys of a block one warp visits
@@ -315,26 +317,34 @@ attention_mma_kernel(AttnParams p) {
 }
 
 // out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in order.
-__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd,
-                                         int num_splits) {
-  int token = blockIdx.x / heads, head = blockIdx.x % heads;
-  long long base = ((long long)token * heads + head) * num_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+// One warp per (token, head): lane s holds split s's (max, sum); the weights are then handed
+// round by shuffle while every lane accumulates its own output dims.
+constexpr int COMBINE_WARPS = 4;
+__global__ void __launch_bounds__(COMBINE_WARPS * 32)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd, int num_splits, int pairs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pair = blockIdx.x * COMBINE_WARPS + warp;
+  if (pair >= pairs) return;
+  int token = pair / heads, head = pair % heads;
+  long long base = (long long)pair * num_splits;
+  float ms = lane < num_splits ? part_ml[(base + lane) * 2] : -INFINITY;
+  float ls = lane < num_splits ? part_ml[(base + lane) * 2 + 1] : 0.f;
+  float m = warp_max(ms);
+  float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
   float l = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    float ms = part_ml[(base + s) * 2];
-    if (ms != -INFINITY) l += exp2f(ms - m) * part_ml[(base + s) * 2 + 1];
-  }
+  for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ls, s);     // split order
   float inv = l > 0.f ? 1.f / l : 0.f;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  for (int d0 = 0; d0 < hd; d0 += 32) {          // every lane takes every trip: the shuffles need the whole warp
+    int d = d0 + lane;
     float acc = 0.f;
     for (int s = 0; s < num_splits; ++s) {
-      float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) acc += exp2f(ms - m) * part_o[(base + s) * hd + d];
+      float ws = __shfl_sync(0xffffffffu, w, s);
+      if (d < hd) acc += ws * part_o[(base + s) * hd + d];
     }
-    out[(long long)token * ld_o + (long long)head * hd + d] = __float2bfloat16_rn(acc * inv);
+    if (d < hd) out[(long long)token * ld_o + (long long)head * hd + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -352,7 +362,7 @@ int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStr
     configured = true;
   }
   dim3 grid((unsigned)(q_tiles * p.num_splits), (unsigned)kv_heads, (unsigned)requests);
-  attention_mma_kernel<HD, NWARPS, KSPLIT><<<grid, NWARPS * 32, smem, stream>>>(p);
+  hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
   return hfee_check_launch("attention_mma");
 }
 
@@ -384,7 +394,7 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   HFEE_REQUIRE(group <= 64, "attention_mma: %d query heads per kv head exceed 64", group);
   HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 2 == 0 && ((uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
   HFEE_REQUIRE(requests <= 65535 && kv_heads <= 65535, "attention_mma: too many requests or kv heads for one grid");
-  HFEE_REQUIRE(max_new > 0 && num_splits >= 1, "attention_mma: bad max_new/num_splits");
+  HFEE_REQUIRE(max_new > 0 && num_splits >= 1 && num_splits <= 32, "attention_mma: num_splits must be in 1..32");
   // when 16 rows hold every request's new tokens (decode) the warps split the keys instead
   bool ksplit = max_new * group <= 16;
   int rows = ksplit ? 16 : 64;
@@ -412,8 +422,9 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
     default: return hfee_fail(HFEE_ERR_ARG, "attention_mma: head_dim %d", head_dim);
   }
   if (rc != HFEE_OK || num_splits == 1) return rc;
-  attention_combine_kernel<<<(unsigned)(n_tokens * heads), head_dim >= 128 ? 128 : 64, 0, stream>>>(
-      p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits);
+  int pairs = n_tokens * heads;
+  hfee_launch(attention_combine_kernel, dim3((unsigned)((pairs + COMBINE_WARPS - 1) / COMBINE_WARPS)),
+              dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits, pairs);
   return hfee_check_launch("attention_combine");
 }
 

@@ -21,6 +21,8 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
                       const T* __restrict__ v_pool, PagedCache cache, const int* __restrict__ positions,
                       const int* __restrict__ slot_of_token, T* __restrict__ out, int ld_o, int n, int heads,
                       float scale, int window) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float q_s[WARPS][MAX_HD];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long task = (long long)blockIdx.x * WARPS + warp;
@@ -92,10 +94,10 @@ HFEE_API int hfee_attention_simt(const void* q, int ld_q, const void* k_pool, co
   long long tasks = (long long)n * heads;
   unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (dtype == HFEE_F32)
-    attention_simt_kernel<float><<<blocks, WARPS * 32, 0, stream>>>((const float*)q, ld_q, (const float*)k_pool,
+    hfee_launch(attention_simt_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)q, ld_q, (const float*)k_pool,
         (const float*)v_pool, c, positions, slot_of_token, (float*)out, ld_o, n, heads, scale, window);
   else if (dtype == HFEE_BF16)
-    attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>((const __nv_bfloat16*)q, ld_q,
+    hfee_launch(attention_simt_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)q, ld_q,
         (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, c, positions, slot_of_token,
         (__nv_bfloat16*)out, ld_o, n, heads, scale, window);
   else

@@ -31,6 +31,32 @@ int hfee_check_launch(const char* what);
     if (!(cond)) return hfee_fail(HFEE_ERR_ARG, __VA_ARGS__); \
   } while (0)
 
+// Programmatic dependent launch: every kernel is launched so that it may start while its
+// predecessor in the stream is still running.  A kernel calls pdl_wait() before it touches
+// anything the predecessor wrote (it returns once the predecessor has completed and its writes
+// are visible) and pdl_launch_dependents() to let its own successor start early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 0 when the environment variable HFEE_NO_PDL is set.
+int hfee_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t hfee_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                        Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = hfee_pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Paged cache addressing shared by every kernel that touches the cache.
 // Pool layout of one layer: [num_pages][kv_heads][page_size][head_dim].
 struct PagedCache {

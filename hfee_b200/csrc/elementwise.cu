@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int width, int vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
   int i = blockIdx.x;
   int tok = tokens[i];
   bool ok = tok >= 0 && tok < vocab;
@@ -23,9 +25,9 @@ HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, float* 
   HFEE_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d vocab=%d", n, width, vocab);
   int threads = width >= 256 ? 256 : 64;
   if (dtype == HFEE_F32)
-    embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, out, width, vocab);
+    hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, out, width, vocab);
   else if (dtype == HFEE_BF16)
-    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, width, vocab);
+    hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, out, width, vocab);
   else
     return hfee_fail(HFEE_ERR_ARG, "embed: unknown dtype %d", dtype);
   return hfee_check_launch("embed");
@@ -40,6 +42,8 @@ template <typename TOut, int THREADS>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                const int* __restrict__ rows, TOut* __restrict__ out, int width,
                                float eps, int add_unit) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float partial[THREADS / 32];
   int r = blockIdx.x;
   const float* xr = x + (long long)(rows ? rows[r] : r) * width;
@@ -66,9 +70,9 @@ HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void*
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0, "rmsnorm: bad sizes n=%d width=%d", n, width);
   if (out_dtype == HFEE_F32)
-    rmsnorm_kernel<float, 256><<<n, 256, 0, stream>>>(x, w, rows, (float*)out, width, eps, add_unit);
+    hfee_launch(rmsnorm_kernel<float, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
   else if (out_dtype == HFEE_BF16)
-    rmsnorm_kernel<__nv_bfloat16, 256><<<n, 256, 0, stream>>>(x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
+    hfee_launch(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
   else
     return hfee_fail(HFEE_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
   return hfee_check_launch("rmsnorm");
@@ -81,6 +85,8 @@ HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void*
 // internal/llm/forward.go:185-186.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float2* __restrict__ cs, int n, int half) {
+  pdl_wait();
+  pdl_launch_dependents();
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n * half) return;
   int i = idx / half, j = idx % half;
@@ -94,7 +100,7 @@ HFEE_API int hfee_rope_table(const int* positions, const double* inv_freq, float
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && half > 0, "rope_table: bad sizes n=%d half=%d", n, half);
   int total = n * half;
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)cs, n, half);
+  hfee_launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)cs, n, half);
   return hfee_check_launch("rope_table");
 }
 
@@ -110,6 +116,8 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, int ld_qkv, const f
                                   const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                                   T* __restrict__ q_out, int ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   PagedCache cache, int heads, int rope_dim, int interleaved) {
+  pdl_wait();
+  pdl_launch_dependents();
   int i = blockIdx.x;
   int hd = cache.head_dim, kvh = cache.kv_heads;
   int half = rope_dim / 2;
@@ -171,10 +179,10 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
   dim3 grid((unsigned)n, (unsigned)((items + threads - 1) / threads));
   if (grid.y > 64) grid.y = 64;
   if (dtype == HFEE_F32)
-    rope_cache_kernel<float><<<grid, threads, 0, stream>>>((const float*)qkv, ld_qkv, (const float2*)cs, positions,
+    hfee_launch(rope_cache_kernel<float>, dim3(grid), dim3(threads), 0, stream, (const float*)qkv, ld_qkv, (const float2*)cs, positions,
         slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c, heads, rope_dim, interleaved);
   else if (dtype == HFEE_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
+    hfee_launch(rope_cache_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
         positions, slot_of_token, (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, c,
         heads, rope_dim, interleaved);
   else
@@ -191,6 +199,8 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld_gu, T* __restrict__ h, int ld_h, int n, int inter,
                               int granule) {
+  pdl_wait();
+  pdl_launch_dependents();
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n * inter) return;
   int i = (int)(idx / inter), c = (int)(idx % inter);
@@ -208,9 +218,9 @@ HFEE_API int hfee_swiglu(const void* gu, int ld_gu, void* h, int ld_h, int n, in
   long long total = (long long)n * inter;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == HFEE_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld_gu, (float*)h, ld_h, n, inter, granule);
+    hfee_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, ld_gu, (float*)h, ld_h, n, inter, granule);
   else if (dtype == HFEE_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter, granule);
+    hfee_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter, granule);
   else
     return hfee_fail(HFEE_ERR_ARG, "swiglu: unknown dtype %d", dtype);
   return hfee_check_launch("swiglu");

@@ -21,6 +21,8 @@ template <typename TIn, typename TOut, bool ACCUM>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const TIn* __restrict__ A, long long lda, const TIn* __restrict__ W, long long ldw,
                  TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   int tid = threadIdx.x;
@@ -76,12 +78,12 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (out_dtype == HFEE_F32) {
     if (accumulate)
-      gemm_simt_kernel<TIn, float, true><<<grid, THREADS, 0, stream>>>((const TIn*)A, lda, (const TIn*)W, ldw, (float*)C, ldc, M, N, K);
+      hfee_launch(gemm_simt_kernel<TIn, float, true>, dim3(grid), dim3(THREADS), 0, stream, (const TIn*)A, lda, (const TIn*)W, ldw, (float*)C, ldc, M, N, K);
     else
-      gemm_simt_kernel<TIn, float, false><<<grid, THREADS, 0, stream>>>((const TIn*)A, lda, (const TIn*)W, ldw, (float*)C, ldc, M, N, K);
+      hfee_launch(gemm_simt_kernel<TIn, float, false>, dim3(grid), dim3(THREADS), 0, stream, (const TIn*)A, lda, (const TIn*)W, ldw, (float*)C, ldc, M, N, K);
   } else if (out_dtype == HFEE_BF16) {
     if (accumulate) return hfee_fail(HFEE_ERR_ARG, "gemm_simt: accumulate needs a float32 output");
-    gemm_simt_kernel<TIn, __nv_bfloat16, false><<<grid, THREADS, 0, stream>>>((const TIn*)A, lda, (const TIn*)W, ldw, (__nv_bfloat16*)C, ldc, M, N, K);
+    hfee_launch(gemm_simt_kernel<TIn, __nv_bfloat16, false>, dim3(grid), dim3(THREADS), 0, stream, (const TIn*)A, lda, (const TIn*)W, ldw, (__nv_bfloat16*)C, ldc, M, N, K);
   } else {
     return hfee_fail(HFEE_ERR_ARG, "gemm_simt: unknown output dtype %d", out_dtype);
   }

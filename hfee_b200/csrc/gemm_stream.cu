@@ -37,17 +37,27 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 }
 
 // MT: token tiles of 16; NT: weight-row tiles of 8; NW: warps per CTA (they split K, so the
-// fewer tokens there are, the more warps keep loads in flight).
+// fewer tokens there are, the more warps keep loads in flight).  The grid is persistent: CTA b
+// owns row tiles b, b + gridDim.x, ...; a warp's work is a sequence of load batches that runs
+// across tile boundaries, so the next tile's weights are already in flight while this tile is
+// reduced and written.  The first batch is issued before the wait on the previous kernel:
+// weights do not depend on it.
 template <int MT, int NT, int NW, int EPI, typename TOut>
 __global__ void __launch_bounds__(NW * 32, 2048 / (NW * 32) >= 4 ? 2 : 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
                    long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
   constexpr int ROWS = 8 * NT;
   constexpr int UNROLL = LOADS_IN_FLIGHT / NT;     // k32-steps per batch of loads
+  constexpr int STRIDE = NW * UNROLL;              // k32-steps all warps cover per batch
   __shared__ float red[NW][MT * 16][ROWS + 1];
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int g = lane >> 2, c = lane & 3;
-  int n0 = blockIdx.x * ROWS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+
+  const int steps = (K + 31) / 32;                 // k32 blocks in all; warp w takes w, w+NW, ...
+  const int n_tiles = (N + ROWS - 1) / ROWS;
+  const int bpt = (steps + STRIDE - 1) / STRIDE;   // batches per tile
+  const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int total = my_tiles * bpt;
 
   float acc[MT][NT][4];
 #pragma unroll
@@ -57,14 +67,6 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
-  const __nv_bfloat16* wrow[NT];
-  bool wok[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    int r = n0 + nt * 8 + g;
-    wok[nt] = r < N;
-    wrow[nt] = W + (long long)(wok[nt] ? r : 0) * ldw;
-  }
   const __nv_bfloat16* arow[MT][2];
   bool aok[MT][2];
 #pragma unroll
@@ -77,23 +79,29 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
     }
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  const int steps = (K + 31) / 32;                       // k32 blocks in all; warp w takes w, w+NW, ...
   uint4 wv[2][UNROLL][NT];
 
-  auto load_batch = [&](int s0, uint4 (&dst)[UNROLL][NT]) {
+  auto load_batch = [&](int j, uint4 (&dst)[UNROLL][NT]) {
+    const int n0 = ((int)blockIdx.x + (j / bpt) * (int)gridDim.x) * ROWS;
+    const int s0 = warp + (j % bpt) * STRIDE;
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      int k = (s0 + u * NW) * 32 + c * 8;
-      bool kok = (s0 + u * NW) < steps && k < K;
+    for (int nt = 0; nt < NT; ++nt) {
+      const int r = n0 + nt * 8 + g;
+      const bool rok = j < total && r < N;
+      const __nv_bfloat16* wrow = W + (long long)(rok ? r : 0) * ldw;
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) dst[u][nt] = (kok && wok[nt]) ? ld_stream(wrow[nt] + k) : zero;
+      for (int u = 0; u < UNROLL; ++u) {
+        const int k = (s0 + u * NW) * 32 + c * 8;
+        dst[u][nt] = (rok && k < K) ? ld_stream(wrow + k) : zero;
+      }
     }
   };
-  auto compute_batch = [&](int s0, const uint4 (&src)[UNROLL][NT]) {
+  auto compute_batch = [&](int j, const uint4 (&src)[UNROLL][NT]) {
+    const int s0 = warp + (j % bpt) * STRIDE;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      int k = (s0 + u * NW) * 32 + c * 8;
-      bool kok = (s0 + u * NW) < steps && k < K;
+      const int k = (s0 + u * NW) * 32 + c * 8;
+      const bool kok = k < K;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         uint4 lo = (kok && aok[mt][0]) ? __ldg((const uint4*)(arow[mt][0] + k)) : zero;
@@ -106,54 +114,62 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
       }
     }
   };
-
-  // two batches of weight loads are kept in flight: the next one is issued before this one is used
-  constexpr int STRIDE = NW * UNROLL;
-  load_batch(warp, wv[0]);
-  for (int s0 = warp; s0 < steps; s0 += 2 * STRIDE) {
-    load_batch(s0 + STRIDE, wv[1]);
-    compute_batch(s0, wv[0]);
-    if (s0 + STRIDE < steps) {
-      load_batch(s0 + 2 * STRIDE, wv[0]);
-      compute_batch(s0 + STRIDE, wv[1]);
+  // After a tile's last batch: add the warps' partial sums in warp order and write the tile.
+  auto finish_tile = [&](int j) {
+    if (j % bpt != bpt - 1) return;
+    const int n0 = ((int)blockIdx.x + (j / bpt) * (int)gridDim.x) * ROWS;
+    // fragment -> shared: c0,c1 = (token g, rows 2c,2c+1); c2,c3 = (token g+8, same rows)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        red[warp][mt * 16 + g][nt * 8 + 2 * c] = acc[mt][nt][0];
+        red[warp][mt * 16 + g][nt * 8 + 2 * c + 1] = acc[mt][nt][1];
+        red[warp][mt * 16 + g + 8][nt * 8 + 2 * c] = acc[mt][nt][2];
+        red[warp][mt * 16 + g + 8][nt * 8 + 2 * c + 1] = acc[mt][nt][3];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+      }
+    __syncthreads();
+    if constexpr (EPI == EPI_SWIGLU) {
+      // rows of a group of 8: [gate x4 | up x4] -> 4 outputs at columns (n0/2 + group*4 ..)
+      constexpr int OUTS = ROWS / 2;
+      for (int idx = threadIdx.x; idx < MT * 16 * OUTS; idx += NW * 32) {
+        int t = idx / OUTS, o = idx % OUTS;
+        int col = n0 / 2 + o;
+        if (t >= M || col >= N / 2) continue;
+        int gr = (o / 4) * 8 + (o % 4);
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) { gate += red[w][t][gr]; up += red[w][t][gr + 4]; }
+        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < MT * 16 * ROWS; idx += NW * 32) {
+        int t = idx / ROWS, r = idx % ROWS;
+        if (t >= M || n0 + r >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) v += red[w][t][r];
+        long long o = (long long)t * ldc + n0 + r;
+        if constexpr (EPI == EPI_ACCUM) C[o] = to_f32<TOut>(C[o]) + v;
+        else C[o] = from_f32<TOut>(v);
+      }
     }
-  }
+    __syncthreads();
+  };
 
-  // fragment -> shared: c0,c1 = (token g, rows 2c,2c+1); c2,c3 = (token g+8, same rows)
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      red[warp][mt * 16 + g][nt * 8 + 2 * c] = acc[mt][nt][0];
-      red[warp][mt * 16 + g][nt * 8 + 2 * c + 1] = acc[mt][nt][1];
-      red[warp][mt * 16 + g + 8][nt * 8 + 2 * c] = acc[mt][nt][2];
-      red[warp][mt * 16 + g + 8][nt * 8 + 2 * c + 1] = acc[mt][nt][3];
-    }
-  __syncthreads();
-
-  if constexpr (EPI == EPI_SWIGLU) {
-    // rows of a group of 8: [gate x4 | up x4] -> 4 outputs at columns (n0/2 + group*4 ..)
-    constexpr int OUTS = ROWS / 2;
-    for (int idx = threadIdx.x; idx < MT * 16 * OUTS; idx += NW * 32) {
-      int t = idx / OUTS, o = idx % OUTS;
-      int col = n0 / 2 + o;
-      if (t >= M || col >= N / 2) continue;
-      int gr = (o / 4) * 8 + (o % 4);
-      float gate = 0.f, up = 0.f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) { gate += red[w][t][gr]; up += red[w][t][gr + 4]; }
-      C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
-    }
-  } else {
-    for (int idx = threadIdx.x; idx < MT * 16 * ROWS; idx += NW * 32) {
-      int t = idx / ROWS, r = idx % ROWS;
-      if (t >= M || n0 + r >= N) continue;
-      float v = 0.f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v += red[w][t][r];
-      long long o = (long long)t * ldc + n0 + r;
-      if constexpr (EPI == EPI_ACCUM) C[o] = to_f32<TOut>(C[o]) + v;
-      else C[o] = from_f32<TOut>(v);
+  load_batch(0, wv[0]);
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int j = 0; j < total; j += 2) {
+    load_batch(j + 1, wv[1]);
+    compute_batch(j, wv[0]);
+    finish_tile(j);
+    if (j + 1 < total) {
+      load_batch(j + 2, wv[0]);
+      compute_batch(j + 1, wv[1]);
+      finish_tile(j + 1);
     }
   }
 }
@@ -163,8 +179,17 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
            int epilogue, int M, int N, int K, cudaStream_t stream) {
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-  unsigned grid = (unsigned)((N + 8 * NT - 1) / (8 * NT));
-#define HFEE_GO(EPI, T) gemm_stream_kernel<MT, NT, NW, EPI, T><<<grid, NW * 32, 0, stream>>>(a, lda, w, ldw, (T*)C, ldc, M, N, K)
+  static int resident = 0;                       // CTAs of this instantiation the whole GPU holds at once
+  if (resident == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<MT, NT, NW, EPI_STORE, float>, NW * 32, 0);
+    resident = (sms > 0 ? sms : 148) * (per_sm > 0 ? per_sm : 1);
+  }
+  int n_tiles = (N + 8 * NT - 1) / (8 * NT);
+  unsigned grid = (unsigned)(n_tiles < resident ? n_tiles : resident);
+#define HFEE_GO(EPI, T) hfee_launch(gemm_stream_kernel<MT, NT, NW, EPI, T>, dim3(grid), dim3(NW * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K)
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
     HFEE_GO(EPI_ACCUM, float);

@@ -140,6 +140,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // barriers and tensor memory are set up while the previous kernel may still run; its output
+  // (A, and C when accumulating) is touched only from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -298,7 +302,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
     configured = true;
   }
   dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));     // M tiles fastest: a W tile is shared in L2
-  gemm_tc_kernel<BN, EPI, TOut><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(ma, mw, (TOut*)C, ldc, M, N, K, status);
+  hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, (TOut*)C, ldc, M, N, K, status);
   return hfee_check_launch("gemm_tcgen05");
 }
 

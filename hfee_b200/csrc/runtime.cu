@@ -1,6 +1,7 @@
 // Error reporting and small host-side helpers of the kernel library.
 #include "common.cuh"
 #include <stdarg.h>
+#include <stdlib.h>
 
 static thread_local char g_error[512] = "";
 
@@ -26,4 +27,10 @@ HFEE_API int hfee_device_is_sm100() {
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
   return major == 10;
+}
+
+int hfee_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) enabled = getenv("HFEE_NO_PDL") == nullptr ? 1 : 0;
+  return enabled;
 }

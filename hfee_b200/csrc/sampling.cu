@@ -13,6 +13,8 @@ constexpr int THREADS = 256;
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const double* __restrict__ uniform, int* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_val[THREADS];
   __shared__ int s_idx[THREADS];
   __shared__ double s_sum[THREADS];
@@ -82,6 +84,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
 // lower index in both stages, so the result is the first maximum.
 __global__ void __launch_bounds__(THREADS)
 argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int chunks, float* __restrict__ part) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_val[THREADS];
   __shared__ int s_idx[THREADS];
   int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
@@ -115,6 +119,8 @@ argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int 
 }
 
 __global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
   int r = blockIdx.x;
   if (threadIdx.x != 0) return;
   float best = -INFINITY;
@@ -136,8 +142,8 @@ HFEE_API int hfee_argmax(const float* logits, long long ld, int M, int V, int ch
   HFEE_REQUIRE(M > 0 && V > 0 && ld >= V && chunks > 0 && chunks <= 1024 && scratch != nullptr,
                "argmax: bad sizes M=%d V=%d chunks=%d", M, V, chunks);
   HFEE_REQUIRE(M <= 65535, "argmax: too many rows");
-  argmax_stage1_kernel<<<dim3((unsigned)chunks, (unsigned)M), THREADS, 0, stream>>>(logits, ld, V, chunks, scratch);
-  argmax_stage2_kernel<<<M, 32, 0, stream>>>(scratch, V, chunks, out);
+  hfee_launch(argmax_stage1_kernel, dim3(dim3((unsigned)chunks, (unsigned)M)), dim3(THREADS), 0, stream, logits, ld, V, chunks, scratch);
+  hfee_launch(argmax_stage2_kernel, dim3(M), dim3(32), 0, stream, scratch, V, chunks, out);
   return hfee_check_launch("argmax");
 }
 
@@ -146,6 +152,6 @@ HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const 
   if (M == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && V > 0 && ld >= V, "sample: bad sizes M=%d V=%d ld=%lld", M, V, ld);
   HFEE_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures need uniform numbers");
-  sample_kernel<<<M, THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out);
+  hfee_launch(sample_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, temperature, uniform, out);
   return hfee_check_launch("sample");
 }
