@@ -244,19 +244,30 @@ def main():
             points[f"decode_b{b}"] = round(decode_point(b, min(args.steps, 32), args.warmup)["tok_s"], 1)
 
     # ---------------------------------------------------------------- end to end through generate()
+    # Host tokens in, host tokens out: every step copies its token ids and positions from pinned
+    # host memory and reads the sampled ids back.  Prompts are read first; the timed window opens
+    # when every request has produced `warmup` tokens (all are decoding by then) and closes when
+    # the first one ends, so it holds decode steps of the full batch only.
     e2e = None
     if not args.no_e2e:
         prompts = [rng.integers(0, vocab, size=PROMPT).tolist() for _ in range(args.batch)]
         opts = SamplingOptions.greedy(num_predict=args.warmup + args.steps)
-        h0, d0 = engine.h2d_bytes, engine.d2h_bytes
-        steps_before = runner.steps_run
-        res = engine.generate(prompts, opts)
-        n_steps = max(1, runner.steps_run - steps_before)
-        eval_tokens = sum(r.stats.eval_tokens for r in res)
-        eval_s = max(r.stats.eval_seconds for r in res)
-        e2e = {"value": round(eval_tokens / eval_s, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": round((engine.h2d_bytes - h0) / n_steps, 1),
-               "d2h_bytes_per_step": round((engine.d2h_bytes - d0) / n_steps, 1)}
+        counts = [0] * args.batch
+        marks = {}
+
+        def on_token(i, tok):
+            counts[i] += 1
+            if "start" not in marks and min(counts) >= args.warmup:
+                marks["start"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
+            if "start" in marks and "end" not in marks and max(counts) >= args.warmup + args.steps:
+                marks["end"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
+
+        engine.generate(prompts, opts, on_token=on_token)
+        (t0_, n0_, h0, d0, s0), (t1_, n1_, h1, d1, s1) = marks["start"], marks["end"]
+        n_steps = max(1, s1 - s0)
+        e2e = {"value": round((n1_ - n0_) / (t1_ - t0_), 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": round((h1 - h0) / n_steps, 1),
+               "d2h_bytes_per_step": round((d1 - d0) / n_steps, 1), "steps": n_steps}
 
     achieved = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
     out = {

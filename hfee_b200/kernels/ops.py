@@ -32,6 +32,7 @@ _SIGNATURES = {
     "hfee_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "hfee_swiglu": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_gemm_stream_norm": [_P, _L, _P, _P, _F, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
@@ -260,6 +261,64 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
     _check(lib.hfee_gemm_tcgen05(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                  _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, block_n,
                                  _status().data_ptr(), _stream()), lib)
+
+
+def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,
+                     epilogue: int = EPI_STORE, rows: Optional[torch.Tensor] = None, add_unit: bool = False) -> None:
+    """:func:`gemm_stream` with the RMS norm fused in front: the token operand is
+    bf16(x[rows] * rsqrt(mean(x^2) + eps) * norm_weight) made on the fly from float32 rows."""
+    lib = library()
+    _i32(rows, "rows")
+    k = x.shape[1]
+    m = rows.numel() if rows is not None else x.shape[0]
+    n = w.shape[0]
+    assert x.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
+    assert w.shape[1] == k and w.dtype == torch.bfloat16
+    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    _check(lib.hfee_gemm_stream_norm(x.data_ptr(), _rows(x, "x"), _ptr(rows), norm_weight.data_ptr(), float(eps),
+                                     int(add_unit), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
+                                     _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
+
+
+# Norming inside the streaming GEMM saves a launch but makes every CTA re-read and re-norm the
+# float32 rows from L2 within its load loop; measured on B200 at batch 8 the decode step went from
+# 1.06 ms to 1.46 ms, so the fusion is off and the norm kernel runs on its own.
+FUSE_NORM_INTO_STREAM_GEMM = False
+
+
+def _norm_fusable(inp, w: torch.Tensor) -> bool:
+    """True when ``inp`` (a lazily normed input, see parts/norm.py) can be normed inside the streaming GEMM."""
+    if not FUSE_NORM_INTO_STREAM_GEMM:
+        return False
+    p = inp.fused_params()
+    x = inp.source
+    return (p is not None and inp.out_dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and inp.n <= STREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and _rows(x, "x") % 4 == 0
+            and _rows(w, "w") % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and p[0].data_ptr() % 16 == 0)
+
+
+def linear_normed(inp, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (+)= norm(x) @ w.T where ``inp`` is a lazily normed input: the norm runs inside the
+    product when a kernel that can do so fits, else ``inp`` is materialised first."""
+    if isinstance(inp, torch.Tensor):
+        linear(inp, w, out, accumulate)
+    elif _norm_fusable(inp, w):
+        weight, eps, add_unit = inp.fused_params()
+        gemm_stream_norm(inp.source, weight, eps, w, out, EPI_ACCUM if accumulate else EPI_STORE, inp.rows, add_unit)
+    else:
+        linear(inp.tensor(), w, out, accumulate)
+
+
+def linear_swiglu_normed(inp, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int, scratch: torch.Tensor) -> None:
+    """:func:`linear_swiglu` on a lazily normed input."""
+    if isinstance(inp, torch.Tensor):
+        linear_swiglu(inp, w_gate_up, out, granule, scratch)
+    elif granule == SWIGLU_GRANULE and w_gate_up.shape[0] % 8 == 0 and _norm_fusable(inp, w_gate_up):
+        weight, eps, add_unit = inp.fused_params()
+        gemm_stream_norm(inp.source, weight, eps, w_gate_up, out, EPI_SWIGLU, inp.rows, add_unit)
+    else:
+        linear_swiglu(inp.tensor(), w_gate_up, out, granule, scratch)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -24,6 +24,8 @@ class PagedAttention(Mixer):
     ``window`` (None = all keys, else the last ``window`` positions), ``scale``
     (None = head_dim**-0.5, internal/llm/forward.go:149)."""
 
+    accepts_lazy_input = True        # the input norm may be fused into the q/k/v projection
+
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
         q, kv = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
@@ -57,11 +59,11 @@ class PagedAttention(Mixer):
         q = rt.scratch("attn_q", (rt.max_tokens, self.q_cols))[:n]
         if writes_cache:
             qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n]
-            ops.linear(xn, self.w_qkv, qkv)
+            ops.linear_normed(xn, self.w_qkv, qkv)
             k_pool, v_pool = cache.k, cache.v
         else:       # reads the cache another run filled: only the queries are needed
             qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n, :self.q_cols]
-            ops.linear(xn, self.w_qkv[:self.q_cols], qkv)
+            ops.linear_normed(xn, self.w_qkv[:self.q_cols], qkv)
             k_pool = v_pool = None
         ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
                              cache.page_size, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,

@@ -6,6 +6,7 @@ from typing import Any
 import torch
 
 from .base import Part, register_part
+from .norm import LazyNormed
 
 
 class PreNormBlock(Part):
@@ -22,10 +23,15 @@ class PreNormBlock(Part):
 
     def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
         xn = self.rt.scratch("block_normed", (self.rt.max_tokens, self.width))[:step.n]
-        self.mixer_norm.forward(residual, xn)
-        self.mixer.forward(xn, residual, step, cache, writes_cache)
-        self.ffn_norm.forward(residual, xn)
-        self.feed_forward.forward(xn, residual, step)
+        self.mixer.forward(self._normed(self.mixer, self.mixer_norm, residual, xn), residual, step, cache, writes_cache)
+        self.feed_forward.forward(self._normed(self.feed_forward, self.ffn_norm, residual, xn), residual, step)
+
+    @staticmethod
+    def _normed(consumer, norm, residual, buffer):
+        """The consumer's input: a lazily normed one if it says it can take it (and may fuse the
+        norm into its first product), else the normed tensor."""
+        lazy = LazyNormed(norm, residual, buffer)
+        return lazy if getattr(consumer, "accepts_lazy_input", False) else lazy.tensor()
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -48,8 +48,13 @@ class LinearHead(Part):
         else:
             self.weight = tensors["weight"]
 
-    def forward(self, xn: torch.Tensor, logits: torch.Tensor) -> None:
-        ops.linear(xn, self.weight, logits)
+    accepts_lazy_input = True        # the final norm may be fused into the product
+
+    def forward(self, xn, logits: torch.Tensor) -> None:
+        if isinstance(xn, torch.Tensor):
+            ops.linear(xn, self.weight, logits)
+        else:
+            ops.linear_normed(xn, self.weight, logits)
 
 
 register_part("embedding", "token", TokenEmbedding)

@@ -15,6 +15,7 @@ from .base import Part, register_part
 class SwiGLUFeedForward(Part):
     """spec: ``width``, ``inner`` (intermediate size)."""
     category = "feed_forward"
+    accepts_lazy_input = True        # the input norm may be fused into the gate/up projection
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
@@ -41,7 +42,7 @@ class SwiGLUFeedForward(Part):
         n, rt = step.n, self.rt
         gu = rt.scratch("ffn_gate_up", (rt.max_tokens, 2 * self.inner))[:n]
         h = rt.scratch("ffn_hidden", (rt.max_tokens, self.inner))[:n]
-        ops.linear_swiglu(xn, self.w_gate_up, h, self.granule, gu)
+        ops.linear_swiglu_normed(xn, self.w_gate_up, h, self.granule, gu)
         ops.linear(h, self.w_down, residual, accumulate=True)
 
 

@@ -15,6 +15,7 @@ import torch
 from ..config.spec import LayerSpec, ModelSpec, PartSpec, check_schedule
 from ..weights.loader import Checkpoint, TensorNeed
 from .base import Runtime, build_part, part_class
+from .norm import LazyNormed
 
 _LAYER_PARTS = (("mixer", "mixer"), ("feed_forward", "ffn"), ("norm", "mixer_norm"), ("norm", "ffn_norm"))
 
@@ -111,7 +112,7 @@ class DecoderModel:
         if m == 0:
             return None
         xn = rt.scratch("head_normed", (rt.max_tokens, self.width))[:m]
-        self.final_norm.forward(residual, xn, rows=step.logit_rows)
+        lazy = LazyNormed(self.final_norm, residual, xn, rows=step.logit_rows)
         logits = rt.scratch("logits", (step.logits_capacity, self.vocab), torch.float32)[:m]
-        self.head.forward(xn, logits)
+        self.head.forward(lazy if getattr(self.head, "accepts_lazy_input", False) else lazy.tensor(), logits)
         return logits

@@ -31,4 +31,34 @@ class RMSNorm(Part):
         ops.rmsnorm(x, self.weight, out, self.eps, rows=rows, add_unit=self.add_unit)
 
 
+    def fused_params(self):
+        """(weight, eps, add_unit): what a kernel needs to apply this norm itself."""
+        return self.weight, self.eps, self.add_unit
+
+
+class LazyNormed:
+    """The normed input of a mixer, feed-forward or head that has not been computed yet.
+
+    A part that can fuse the norm into its first matrix product hands this object to
+    ``ops.linear_normed``; any other use calls :meth:`tensor`, which runs the norm once into
+    ``buffer`` and returns it.  ``rows`` gathers source rows (the head norms only the rows whose
+    logits are wanted)."""
+
+    def __init__(self, norm, source: torch.Tensor, buffer: torch.Tensor, rows: Optional[torch.Tensor] = None):
+        self.norm, self.source, self.buffer, self.rows = norm, source, buffer, rows
+        self.n = buffer.shape[0]
+        self.out_dtype = buffer.dtype
+        self._done = False
+
+    def fused_params(self):
+        f = getattr(self.norm, "fused_params", None)
+        return f() if f is not None else None
+
+    def tensor(self) -> torch.Tensor:
+        if not self._done:
+            self.norm.forward(self.source, self.buffer, rows=self.rows)
+            self._done = True
+        return self.buffer
+
+
 register_part("norm", "rms_norm", RMSNorm)

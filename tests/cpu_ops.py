@@ -105,11 +105,19 @@ def sample(logits, out, temperature=None, uniform=None):
             out[r] = int(torch.searchsorted(cum, float(uniform[r]) * float(cum[-1])).clamp(max=logits.shape[1] - 1))
 
 
+def linear_normed(inp, w, out, accumulate=False):
+    linear(inp if isinstance(inp, torch.Tensor) else inp.tensor(), w, out, accumulate)
+
+
+def linear_swiglu_normed(inp, w_gate_up, out, granule, scratch):
+    linear_swiglu(inp if isinstance(inp, torch.Tensor) else inp.tensor(), w_gate_up, out, granule, scratch)
+
+
 def argmax(logits, out, scratch):
     out.copy_(torch.argmax(logits, dim=1).to(torch.int32))
 
 
-ALL = ("argmax", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_swiglu",
+ALL = ("argmax", "linear_normed", "linear_swiglu_normed", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_swiglu",
        "paged_attention", "sample")
 
 

@@ -220,3 +220,36 @@ def test_sample_greedy_and_temperature(ops, m, v):
             got = int(out[i])
             # equal up to rounding of the running sum at the boundary
             assert got == want or abs(float(cum[got] - cum[want])) / float(cum[-1]) < 1e-9
+
+
+@pytest.mark.parametrize("m", [1, 8, 17, 64])
+@pytest.mark.parametrize("n,k", [(24, 40), (96, 2048), (3072, 2048)])
+def test_gemm_stream_with_fused_norm(ops, m, n, k):
+    """The norm fused in front of the product equals norm kernel + product kernel (same bf16
+    rounding of the normed rows), with and without a row gather, for every epilogue."""
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(m + 3, k, generator=g) * 2).to(DEV)
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    rows = torch.tensor([(3 * i + 1) % (m + 3) for i in range(m)], dtype=torch.int32, device=DEV)
+    for idx in (None, rows):
+        src = x if idx is not None else x[:m].contiguous()
+        xn = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
+        ops.rmsnorm(src, nw, xn, 1e-5, rows=idx)
+        want = torch.empty(m, n, dtype=torch.float32, device=DEV)
+        ops.gemm_stream(xn, w, want)
+        got = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_stream_norm(src, nw, 1e-5, w, got, ops.EPI_STORE, idx)
+        # differences come only from rows whose bf16 rounding flips on a last-bit change of 1/rms
+        _close(got, want, 2e-3)
+        s = (src if idx is None else src[idx.long()]).double()
+        ref = (s / torch.sqrt((s * s).mean(1, keepdim=True) + 1e-5) * nw.double()) @ w.double().t()
+        _close(got, ref, 6e-3)
+    if n % 8 == 0:
+        out = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_stream_norm(x[:m].contiguous(), nw, 1e-5, w, out, ops.EPI_SWIGLU)
+        s = x[:m].double()
+        y = ((s / torch.sqrt((s * s).mean(1, keepdim=True) + 1e-5) * nw.double()).to(torch.bfloat16).double()) @ w.double().t()
+        y = y.reshape(m, n // 8, 2, 4)
+        gate, up = y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)
+        _close(out, gate / (1 + torch.exp(-gate)) * up, 6e-3)
