@@ -29,8 +29,8 @@ class EngineConfig:
             self.dtype = "float32"
         else:
             raise ValueError(f"dtype must be bfloat16 or float32, got {self.dtype!r}")
-        if self.page_size <= 0 or self.page_size % 16:
-            raise ValueError(f"page_size must be a positive multiple of 16, got {self.page_size}")
+        if self.page_size < 16 or self.page_size & (self.page_size - 1):
+            raise ValueError(f"page_size must be a power of two of at least 16, got {self.page_size}")
         if self.max_requests <= 0 or self.max_context <= 0 or self.max_batch_tokens <= 0:
             raise ValueError("max_requests, max_context and max_batch_tokens must be positive")
         if self.max_cache_tokens is None:

@@ -70,12 +70,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // KSPLIT = false: each warp owns 16 query rows and visits all 64 keys of a block (prefill).
 // KSPLIT = true: the tile has 16 rows; each warp visits 16 of a block's 64 keys with a softmax
 // state of its own, and the warps' results are merged at the end (decode: few rows, many keys).
-template <int HD, int NWARPS, bool KSPLIT>
+// STAGES key/value blocks are in flight per CTA (cp.async groups): decode CTAs, which do little
+// arithmetic per block, keep more of them in flight than prefill CTAs.
+template <int HD, int NWARPS, bool KSPLIT, int STAGES>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_mma_kernel(AttnParams p) {
-  pdl_wait();
-  pdl_launch_dependents();
   static_assert(!KSPLIT || NWARPS * 16 == BLOCK_N, "key-split mode needs 16 keys per warp");
+  static_assert(STAGES >= 2, "at least double buffering");
   constexpr int ROWS = KSPLIT ? 16 : 16 * NWARPS;
   constexpr int WKEYS = KSPLIT ? 16 : BLOCK_N;        // keys of a block one warp visits
   constexpr int PITCH = HD + 8;                 // elements; odd number of 16-byte units: conflict-free ldmatrix
@@ -83,8 +84,8 @@ attention_mma_kernel(AttnParams p) {
   constexpr int THREADS = NWARPS * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [ROWS][PITCH]
-  __nv_bfloat16* k_s = q_s + ROWS * PITCH;                                // [2][BLOCK_N][PITCH]
-  __nv_bfloat16* v_s = k_s + 2 * BLOCK_N * PITCH;                         // [2][BLOCK_N][PITCH]
+  __nv_bfloat16* k_s = q_s + ROWS * PITCH;                                // [STAGES][BLOCK_N][PITCH]
+  __nv_bfloat16* v_s = k_s + STAGES * BLOCK_N * PITCH;                    // [STAGES][BLOCK_N][PITCH]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -110,6 +111,16 @@ attention_mma_kernel(AttnParams p) {
     b_hi = min(b_hi, b_lo + per - 1);
   }
 
+  // The batch layout and the block table come from the host, not from the previous kernel: they
+  // were read (and the table rows of this CTA's blocks pulled into cache) while that kernel may
+  // still be running.  Queries and this step's keys/values are its output: wait for it now.
+  if (b_lo <= b_hi && tid <= b_hi - b_lo) {
+    int warm = p.cache.block_table[(long long)slot * p.cache.max_pages + (b_lo + tid) * BLOCK_N / p.cache.page_size];
+    asm volatile("" ::"r"(warm));
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+
   // ---- stage Q (rows beyond rows_used are zero)
   for (int idx = tid; idx < ROWS * CHUNKS; idx += THREADS) {
     int row = idx / CHUNKS, ch = idx % CHUNKS;
@@ -120,16 +131,30 @@ attention_mma_kernel(AttnParams p) {
     cp_async16(q_s + row * PITCH + ch * 8, src, ok);
   }
 
+  // A block's 64 rows x CHUNKS 16-byte pieces are spread over the threads.  Page ids are looked
+  // up first for all of a thread's pieces (independent loads), then the copies are issued.
+  constexpr int PIECES = (BLOCK_N * CHUNKS + THREADS - 1) / THREADS;
   auto load_kv = [&](int block, int stage) {
     __nv_bfloat16* kd = k_s + stage * BLOCK_N * PITCH;
     __nv_bfloat16* vd = v_s + stage * BLOCK_N * PITCH;
-    for (int idx = tid; idx < BLOCK_N * CHUNKS; idx += THREADS) {
-      int row = idx / CHUNKS, ch = idx % CHUNKS;
-      int pos = block * BLOCK_N + row;
-      bool ok = pos >= key_lo && pos <= pos_last;
-      long long off = ok ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
-      cp_async16(kd + row * PITCH + ch * 8, p.k_pool + off, ok);
-      cp_async16(vd + row * PITCH + ch * 8, p.v_pool + off, ok);
+    long long off[PIECES];
+    bool ok[PIECES];
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      const int idx = tid + i * THREADS;
+      const int row = idx / CHUNKS, ch = idx % CHUNKS;
+      const int pos = block * BLOCK_N + row;
+      ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
+      off[i] = ok[i] ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      const int idx = tid + i * THREADS;
+      if (idx < BLOCK_N * CHUNKS) {
+        const int row = idx / CHUNKS, ch = idx % CHUNKS;
+        cp_async16(kd + row * PITCH + ch * 8, p.k_pool + off[i], ok[i]);
+        cp_async16(vd + row * PITCH + ch * 8, p.v_pool + off[i], ok[i]);
+      }
     }
   };
 
@@ -148,14 +173,19 @@ attention_mma_kernel(AttnParams p) {
     row_pos[h] = row < rows_used ? pos_first + row / p.group : -1;      // -1: every key masked
   }
 
-  if (b_lo <= b_hi) load_kv(b_lo, 0);
-  cp_async_commit();
+  // one cp.async group per block, committed even when empty, so that "all but the newest
+  // STAGES-1 groups are complete" always means "this iteration's block has landed"
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (b_lo + i <= b_hi) load_kv(b_lo + i, i);
+    cp_async_commit();
+  }
 
   for (int b = b_lo; b <= b_hi; ++b) {
-    int stage = (b - b_lo) & 1;
-    if (b + 1 <= b_hi) load_kv(b + 1, stage ^ 1);
+    int stage = (b - b_lo) % STAGES;
+    if (b + STAGES - 1 <= b_hi) load_kv(b + STAGES - 1, (b - b_lo + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
 
     const __nv_bfloat16* kt = k_s + stage * BLOCK_N * PITCH;
@@ -348,28 +378,33 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
   }
 }
 
-template <int HD, bool KSPLIT>
+template <int HD, bool KSPLIT, int STAGES>
 int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
   constexpr int NWARPS = 4;
   constexpr int PITCH = HD + 8;
   constexpr int ROWS = KSPLIT ? 16 : 64;
-  size_t smem = (size_t)(ROWS + 4 * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
+  size_t smem = (size_t)(ROWS + 2 * STAGES * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS, KSPLIT>,
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid((unsigned)(q_tiles * p.num_splits), (unsigned)kv_heads, (unsigned)requests);
-  hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
+  hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
   return hfee_check_launch("attention_mma");
 }
 
 template <int HD>
 int dispatch_mode(const AttnParams& p, bool ksplit, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
-  if (ksplit) return launch<HD, true>(p, q_tiles, kv_heads, requests, stream);
-  return launch<HD, false>(p, q_tiles, kv_heads, requests, stream);
+  if (!ksplit) return launch<HD, false, 2>(p, q_tiles, kv_heads, requests, stream);
+  // decode: keep four key blocks in flight per CTA when the grid is small enough that the larger
+  // shared-memory footprint (fewer CTAs per SM) does not add a wave; otherwise two
+  constexpr int DEEP = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
+  long long ctas = (long long)p.num_splits * kv_heads * requests;
+  if (DEEP > 2 && ctas <= 3 * 148) return launch<HD, true, DEEP>(p, q_tiles, kv_heads, requests, stream);
+  return launch<HD, true, 2>(p, q_tiles, kv_heads, requests, stream);
 }
 
 }  // namespace
@@ -406,7 +441,8 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   p.q = (const __nv_bfloat16*)q; p.ld_q = ld_q;
   p.out = (__nv_bfloat16*)out; p.ld_o = ld_o;
   p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
-  p.cache = PagedCache{block_table, max_pages, page_size, kv_heads, head_dim, (long long)kv_heads * page_size * head_dim};
+  HFEE_REQUIRE(make_paged_cache(&p.cache, block_table, max_pages, page_size, kv_heads, head_dim),
+               "attention_mma: page_size %d must be a power of two", page_size);
   p.cu_tokens = cu_tokens; p.slots = slots; p.context_before = context_before;
   p.heads = heads; p.group = group;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -90,7 +90,9 @@ HFEE_API int hfee_attention_simt(const void* q, int ld_q, const void* k_pool, co
   HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                "attention_simt: heads %d must be a multiple of kv_heads %d", heads, kv_heads);
   HFEE_REQUIRE(page_size > 0 && max_pages > 0, "attention_simt: bad cache sizes");
-  PagedCache c{block_table, max_pages, page_size, kv_heads, head_dim, (long long)kv_heads * page_size * head_dim};
+  PagedCache c;
+  HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
+               "page_size %d must be a power of two", page_size);
   long long tasks = (long long)n * heads;
   unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (dtype == HFEE_F32)

@@ -62,15 +62,28 @@ cudaError_t hfee_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t 
 struct PagedCache {
   const int* block_table;   // [max_requests][max_pages] page ids, row = request slot
   int max_pages;            // row length of block_table
-  int page_size;
+  int page_size;            // a power of two
+  int page_shift;           // log2(page_size)
   int kv_heads;
   int head_dim;
   long long page_stride;    // elements per page = kv_heads*page_size*head_dim
 };
 
+// Fills a PagedCache; returns false if page_size is not a power of two.
+inline bool make_paged_cache(PagedCache* c, const int* block_table, int max_pages, int page_size, int kv_heads,
+                             int head_dim) {
+  if (page_size <= 0 || (page_size & (page_size - 1)) != 0) return false;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  *c = PagedCache{block_table, max_pages, page_size, shift, kv_heads, head_dim,
+                  (long long)kv_heads * page_size * head_dim};
+  return true;
+}
+
 __device__ __forceinline__ long long paged_offset(const PagedCache& c, int slot, int pos, int kv_head) {
-  int page = c.block_table[(long long)slot * c.max_pages + pos / c.page_size];
-  return (long long)page * c.page_stride + ((long long)kv_head * c.page_size + pos % c.page_size) * c.head_dim;
+  int page = c.block_table[(long long)slot * c.max_pages + (pos >> c.page_shift)];
+  return (long long)page * c.page_stride +
+         ((long long)kv_head * c.page_size + (pos & (c.page_size - 1))) * c.head_dim;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

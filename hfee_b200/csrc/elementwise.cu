@@ -116,14 +116,16 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, int ld_qkv, const f
                                   const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                                   T* __restrict__ q_out, int ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   PagedCache cache, int heads, int rope_dim, int interleaved) {
-  pdl_wait();
-  pdl_launch_dependents();
   int i = blockIdx.x;
   int hd = cache.head_dim, kvh = cache.kv_heads;
   int half = rope_dim / 2;
   int per_block = (int)blockDim.x * gridDim.y;    // work items are spread over the blocks of grid.y
-  int pos = positions[i];
+  int pos = positions[i];                          // host-written: readable before the previous kernel ends
   int slot = slot_of_token[i];
+  int page_warm = k_pool ? cache.block_table[(long long)slot * cache.max_pages + pos / cache.page_size] : 0;
+  asm volatile("" ::"r"(page_warm));
+  pdl_wait();
+  pdl_launch_dependents();
   const T* row = qkv + (long long)i * ld_qkv;
   int total_heads = k_pool ? heads + 2 * kvh : heads;   // q only when this run reads another run's cache
   // one work item = (head, pair index within the head); hd/2 items per head
@@ -172,8 +174,9 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
   HFEE_REQUIRE(rope_dim >= 0 && rope_dim <= head_dim && rope_dim % 2 == 0,
                "rope: rope_dim %d must be even and at most head_dim %d", rope_dim, head_dim);
   HFEE_REQUIRE(heads > 0 && kv_heads > 0 && page_size > 0 && max_pages > 0, "rope: bad sizes");
-  PagedCache c{block_table, max_pages, page_size, kv_heads, head_dim,
-               (long long)kv_heads * page_size * head_dim};
+  PagedCache c;
+  HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
+               "page_size %d must be a power of two", page_size);
   int threads = 256;
   int items = (heads + 2 * kv_heads) * (head_dim / 2);
   dim3 grid((unsigned)n, (unsigned)((items + threads - 1) / threads));

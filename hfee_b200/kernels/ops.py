@@ -370,8 +370,8 @@ MAX_SPLITS = 32
 
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
     """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
-    every SM about four CTAs, at least two key blocks of 64 each."""
-    want = -(-4 * SM_COUNT // max(1, requests * kv_heads))
+    every SM the three CTAs it can hold at head size 64, at least two key blocks of 64 each."""
+    want = -(-3 * SM_COUNT // max(1, requests * kv_heads))
     return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 
