@@ -104,9 +104,11 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
   const uint4 zero = make_uint4(0, 0, 0, 0);
   uint4 wv[2][UNROLL][NT];
 
-  auto load_batch = [&](int j, uint4 (&dst)[UNROLL][NT]) {
-    const int n0 = ((int)blockIdx.x + (j / bpt) * (int)gridDim.x) * ROWS;
-    const int s0 = warp + (j % bpt) * STRIDE;
+  // batch j of this CTA = batch (j % bpt) of its tile number (j / bpt); the loop below keeps
+  // those two as counters instead of dividing
+  auto load_batch = [&](int j, int tile_no, int in_tile, uint4 (&dst)[UNROLL][NT]) {
+    const int n0 = ((int)blockIdx.x + tile_no * (int)gridDim.x) * ROWS;
+    const int s0 = warp + in_tile * STRIDE;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int r = n0 + nt * 8 + g;
@@ -119,8 +121,8 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
       }
     }
   };
-  auto compute_batch = [&](int j, const uint4 (&src)[UNROLL][NT]) {
-    const int s0 = warp + (j % bpt) * STRIDE;
+  auto compute_batch = [&](int in_tile, const uint4 (&src)[UNROLL][NT]) {
+    const int s0 = warp + in_tile * STRIDE;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (s0 + u * NW) * 32 + c * 8;
@@ -164,9 +166,8 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
     }
   };
   // After a tile's last batch: add the warps' partial sums in warp order and write the tile.
-  auto finish_tile = [&](int j) {
-    if (j % bpt != bpt - 1) return;
-    const int n0 = ((int)blockIdx.x + (j / bpt) * (int)gridDim.x) * ROWS;
+  auto finish_tile = [&](int tile_no) {
+    const int n0 = ((int)blockIdx.x + tile_no * (int)gridDim.x) * ROWS;
     // fragment -> shared: c0,c1 = (token g, rows 2c,2c+1); c2,c3 = (token g+8, same rows)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -208,7 +209,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
     __syncthreads();
   };
 
-  load_batch(0, wv[0]);
+  load_batch(0, 0, 0, wv[0]);
   pdl_wait();
   pdl_launch_dependents();
   if constexpr (NORM) {
@@ -238,14 +239,154 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
         }
       }
   }
+  int tile_no = 0, in_tile = 0;                 // of the batch being computed
+  auto next = [&](int& t, int& b) { if (++b == bpt) { b = 0; ++t; } };
   for (int j = 0; j < total; j += 2) {
-    load_batch(j + 1, wv[1]);
-    compute_batch(j, wv[0]);
-    finish_tile(j);
+    int t1 = tile_no, b1 = in_tile;
+    next(t1, b1);
+    load_batch(j + 1, t1, b1, wv[1]);
+    compute_batch(in_tile, wv[0]);
+    if (in_tile == bpt - 1) finish_tile(tile_no);
     if (j + 1 < total) {
-      load_batch(j + 2, wv[0]);
-      compute_batch(j + 1, wv[1]);
-      finish_tile(j + 1);
+      int t2 = t1, b2 = b1;
+      next(t2, b2);
+      load_batch(j + 2, t2, b2, wv[0]);
+      compute_batch(b1, wv[1]);
+      if (b1 == bpt - 1) finish_tile(t1);
+      tile_no = t2;
+      in_tile = b2;
+    }
+  }
+}
+
+// The same product with one warp per tile of 8 weight rows over the whole of K: no partial sums
+// to add across warps, no barriers, for shapes with enough tiles to occupy every warp of the GPU
+// (gate/up and output-head projections).  Warp w of the grid owns tiles w, w + warps, ...; its
+// loads run two batches ahead across tile boundaries.
+constexpr int ROWS_WARPS = 8;                    // warps per CTA
+constexpr int ROWS_UNROLL = 8;                   // 16-byte weight loads per lane in one batch
+
+template <int MT, int EPI, typename TOut>
+__global__ void __launch_bounds__(ROWS_WARPS * 32, 2)
+gemm_stream_rows_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
+                        long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int warps = (int)gridDim.x * ROWS_WARPS;
+  const int first = (int)blockIdx.x * ROWS_WARPS + (threadIdx.x >> 5);
+  const int n_tiles = (N + 7) / 8;
+  const int steps = (K + 31) / 32;
+  const int bpt = (steps + ROWS_UNROLL - 1) / ROWS_UNROLL;
+  const int my_tiles = first < n_tiles ? (n_tiles - 1 - first) / warps + 1 : 0;
+  const int total = my_tiles * bpt;
+
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+  const __nv_bfloat16* arow[MT][2];
+  bool aok[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int t = mt * 16 + h * 8 + g;
+      aok[mt][h] = t < M;
+      arow[mt][h] = A + (long long)(aok[mt][h] ? t : 0) * lda;
+    }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 wv[2][ROWS_UNROLL];
+
+  auto load_batch = [&](int j, int tile_no, int in_tile, uint4 (&dst)[ROWS_UNROLL]) {
+    const int r = (first + tile_no * warps) * 8 + g;
+    const bool rok = j < total && r < N;
+    const __nv_bfloat16* wrow = W + (long long)(rok ? r : 0) * ldw;
+#pragma unroll
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      const int k = (in_tile * ROWS_UNROLL + u) * 32 + c * 8;
+      dst[u] = (rok && k < K) ? ld_stream(wrow + k) : zero;
+    }
+  };
+  auto compute_batch = [&](int in_tile, const uint4 (&src)[ROWS_UNROLL]) {
+#pragma unroll
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      const int k = (in_tile * ROWS_UNROLL + u) * 32 + c * 8;
+      const bool kok = k < K;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint4 lo = (kok && aok[mt][0]) ? __ldg((const uint4*)(arow[mt][0] + k)) : zero;
+        uint4 hi = (kok && aok[mt][1]) ? __ldg((const uint4*)(arow[mt][1] + k)) : zero;
+        mma_bf16(acc[mt], lo.x, hi.x, lo.y, hi.y, src[u].x, src[u].y);
+        mma_bf16(acc[mt], lo.z, hi.z, lo.w, hi.w, src[u].z, src[u].w);
+      }
+    }
+  };
+  // acc[mt] = {(token g, rows 2c, 2c+1), (token g+8, rows 2c, 2c+1)} of the tile
+  auto finish_tile = [&](int tile_no) {
+    const int n0 = (first + tile_no * warps) * 8;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      if constexpr (EPI == EPI_SWIGLU) {
+        // rows 0-3 gate, 4-7 up: lanes c = 0,1 hold gate, c = 2,3 the matching up values
+        float u0 = __shfl_xor_sync(0xffffffffu, acc[mt][0], 2), u1 = __shfl_xor_sync(0xffffffffu, acc[mt][1], 2);
+        float u2 = __shfl_xor_sync(0xffffffffu, acc[mt][2], 2), u3 = __shfl_xor_sync(0xffffffffu, acc[mt][3], 2);
+        if (c < 2) {
+          const int col = n0 / 2 + 2 * c;
+          const float gv[4] = {acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]};
+          const float uv[4] = {u0, u1, u2, u3};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = mt * 16 + h * 8 + g;
+            if (t >= M) continue;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              if (col + e >= N / 2) continue;
+              float gate = gv[2 * h + e], up = uv[2 * h + e];
+              C[(long long)t * ldc + col + e] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = mt * 16 + h * 8 + g;
+          if (t >= M) continue;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = n0 + 2 * c + e;
+            if (col >= N) continue;
+            const long long o = (long long)t * ldc + col;
+            const float v = acc[mt][2 * h + e];
+            if constexpr (EPI == EPI_ACCUM) C[o] = to_f32<TOut>(C[o]) + v;
+            else C[o] = from_f32<TOut>(v);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+    }
+  };
+
+  load_batch(0, 0, 0, wv[0]);
+  pdl_wait();
+  pdl_launch_dependents();
+  int tile_no = 0, in_tile = 0;
+  auto next = [&](int& t, int& b) { if (++b == bpt) { b = 0; ++t; } };
+  for (int j = 0; j < total; j += 2) {
+    int t1 = tile_no, b1 = in_tile;
+    next(t1, b1);
+    load_batch(j + 1, t1, b1, wv[1]);
+    compute_batch(in_tile, wv[0]);
+    if (in_tile == bpt - 1) finish_tile(tile_no);
+    if (j + 1 < total) {
+      int t2 = t1, b2 = b1;
+      next(t2, b2);
+      load_batch(j + 2, t2, b2, wv[0]);
+      compute_batch(b1, wv[1]);
+      if (b1 == bpt - 1) finish_tile(t1);
+      tile_no = t2;
+      in_tile = b2;
     }
   }
 }
@@ -281,6 +422,30 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
 }  // namespace
 
 namespace {
+template <int MT>
+int launch_rows(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
+                int epilogue, int M, int N, int K, cudaStream_t stream) {
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  int n_tiles = (N + 7) / 8;
+  int ctas = (n_tiles + ROWS_WARPS - 1) / ROWS_WARPS;
+  unsigned grid = (unsigned)(ctas < 2 * 148 ? ctas : 2 * 148);
+#define HFEE_GO(EPI, T) hfee_launch(gemm_stream_rows_kernel<MT, EPI, T>, dim3(grid), dim3(ROWS_WARPS * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K)
+  if (epilogue == EPI_ACCUM) {
+    if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
+    HFEE_GO(EPI_ACCUM, float);
+  } else if (epilogue == EPI_SWIGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
+  }
+#undef HFEE_GO
+  return hfee_check_launch("gemm_stream_rows");
+}
+
+// Enough 8-row tiles to give every resident warp (148 SMs x 16) about one: a warp per tile.
+constexpr int ROWS_MIN_TILES = 1536;
+
 template <bool NORM>
 int by_tokens(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
               int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
@@ -309,6 +474,10 @@ HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long 
   if (rc != HFEE_OK) return rc;
   HFEE_REQUIRE(lda % 8 == 0 && lda >= K && (uintptr_t)A % 16 == 0,
                "gemm_stream: the tokens' leading dimension %lld must be a multiple of 8, at least K, and 16-byte aligned", lda);
+  if ((N + 7) / 8 >= ROWS_MIN_TILES && M <= 32) {
+    if (M <= 16) return launch_rows<1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+    return launch_rows<2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  }
   NormArgs none{nullptr, 0, nullptr, nullptr, 0.f, 0};
   return by_tokens<false>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, none, stream);
 }

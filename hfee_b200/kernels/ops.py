@@ -34,6 +34,8 @@ _SIGNATURES = {
     "hfee_gemm_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_stream_norm": [_P, _L, _P, _P, _F, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+    "hfee_gemm_skinny": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _P],
+    "hfee_gemm_skinny_splits": [_I, _I, _I, _L],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -56,6 +58,7 @@ def library() -> ctypes.CDLL:
         raise KernelLibraryError(f"cannot load the sm_100a kernel library: {e}") from e
     lib.hfee_last_error.restype = ctypes.c_char_p
     lib.hfee_device_is_sm100.restype = _I
+    lib.hfee_gemm_skinny_splits.restype = _I
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -321,10 +324,49 @@ def linear_swiglu_normed(inp, w_gate_up: torch.Tensor, out: torch.Tensor, granul
         linear_swiglu(inp.tensor(), w_gate_up, out, granule, scratch)
 
 
+_SKINNY_WS: Optional[torch.Tensor] = None
+SKINNY_WS_FLOATS = 4 << 20
+
+
+def _skinny_workspace() -> torch.Tensor:
+    """Float32 workspace for the partial tiles of K-split skinny products (made once, 16 MiB)."""
+    global _SKINNY_WS
+    if _SKINNY_WS is None:
+        _SKINNY_WS = torch.empty(SKINNY_WS_FLOATS, dtype=torch.float32, device="cuda")
+    return _SKINNY_WS
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """out (+)= a @ w.T for at most 64 rows of ``a`` on tcgen05 with the operands swapped (weight
+    rows on the 128-row side of the MMA) and K split among CTAs when weight tiles are few; TMA
+    streams the weights through a deep shared-memory ring.  Epilogues as in :func:`gemm_stream`."""
+    lib = library()
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
+    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    ws = _skinny_workspace()
+    _check(lib.hfee_gemm_skinny(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
+                                _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, ws.data_ptr(), ws.numel(),
+                                _status().data_ptr(), _stream()), lib)
+    if lib.hfee_gemm_skinny_splits(m, n, k, ws.numel()) > 1:
+        count_launches(1)
+
+
+STREAM_BEST_TOKENS = 16      # up to here the register-streaming kernels win; above, the skinny tcgen05 kernel
+
+
+def _small_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
+    if a.shape[0] <= STREAM_BEST_TOKENS or not USE_TCGEN05:
+        gemm_stream(a, w, out, epilogue)
+    else:
+        gemm_skinny(a, w, out, epilogue)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (+)= a @ w.T, choosing the kernel for the dtype and the shape."""
     if _streamable(a, w):
-        gemm_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+        _small_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     elif USE_TCGEN05 and _tensor_core_ok(a, w):
         gemm_tcgen05(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     else:
@@ -341,7 +383,7 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, g
     projection when it is not fused."""
     fusable = granule == SWIGLU_GRANULE and w_gate_up.shape[0] % 8 == 0
     if fusable and _streamable(a, w_gate_up):
-        gemm_stream(a, w_gate_up, out, EPI_SWIGLU)
+        _small_gemm(a, w_gate_up, out, EPI_SWIGLU)
     elif fusable and USE_TCGEN05 and _tensor_core_ok(a, w_gate_up) and out.dtype == torch.bfloat16:
         gemm_tcgen05(a, w_gate_up, out, EPI_SWIGLU)
     else:
@@ -371,7 +413,7 @@ MAX_SPLITS = 32
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
     """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
     every SM the three CTAs it can hold at head size 64, at least two key blocks of 64 each."""
-    want = -(-3 * SM_COUNT // max(1, requests * kv_heads))
+    want = 3 * SM_COUNT // max(1, requests * kv_heads)
     return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 

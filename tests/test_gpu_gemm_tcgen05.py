@@ -71,3 +71,49 @@ def test_strided_operands():
     ops.gemm_tcgen05(a, w, out)
     ops.check_status()
     assert _err(out, a.double().cpu() @ w.double().cpu().t()) < _f32_tol(128)
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(8, 8), (100, 96), (257, 1000), (2048, 2048), (3072, 2048), (2048, 8192), (16384, 2048)])
+def test_skinny_swapped_operands_every_epilogue(m, n, k):
+    """The few-token tcgen05 product (weights on the MMA's 128-row side, K split among CTAs and
+    added in split order): direct and split paths, ragged edges, every epilogue."""
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    ref = a.double().cpu() @ w.double().cpu().t()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(a, w, out)
+    ops.check_status()
+    assert _err(out, ref) < _f32_tol(k)
+    outb = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(a, w, outb)
+    assert _err(outb, ref) < 6e-3
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_skinny(a, w, acc, ops.EPI_ACCUM)
+    ops.check_status()
+    assert _err(acc, base.double().cpu() + ref) < _f32_tol(k)
+    if n % 8 == 0:
+        y = (ref * 0.1).reshape(m, n // 8, 2, 4)
+        gate, up = y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)
+        w2 = (w.float() * 0.1).to(torch.bfloat16)
+        y2 = (a.double().cpu() @ w2.double().cpu().t()).reshape(m, n // 8, 2, 4)
+        gate, up = y2[:, :, 0].reshape(m, -1), y2[:, :, 1].reshape(m, -1)
+        outs = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_skinny(a, w2, outs, ops.EPI_SWIGLU)
+        ops.check_status()
+        assert _err(outs, gate / (1 + torch.exp(-gate)) * up) < 6e-3
+
+
+def test_skinny_rows_do_not_depend_on_the_batch():
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(40, 2048, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(3072, 2048, generator=g).to(torch.bfloat16).to(DEV)
+    full = torch.empty(40, 3072, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(a, w, full)
+    one = torch.empty(1, 3072, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(a[23:24], w, one)
+    assert torch.equal(one[0], full[23])
