@@ -51,6 +51,12 @@ class _PagedGroup:
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.table_dev = torch.full((max_requests, max_pages), -1, dtype=torch.int32, device=device)
+        # pinned staging copies of the table, used in turn, so that an upload never makes the host
+        # wait for the GPU (a copy from pageable memory would)
+        pin = torch.device(device).type == "cuda"
+        self.staging = [torch.empty((max_requests, max_pages), dtype=torch.int32, pin_memory=pin) for _ in range(4)]
+        self.staging_events = [None] * 4
+        self.staging_turn = 0
 
     def first_needed_page(self, length: int) -> int:
         """First logical page a token at position >= ``length`` can still read."""
@@ -183,7 +189,16 @@ class CacheManager:
         """Copy block tables that changed to the device (before the step that uses them)."""
         for g in self.paged:
             if g.dirty:
-                g.table_dev.copy_(torch.from_numpy(g.table))
+                i = g.staging_turn
+                g.staging_turn = (i + 1) % len(g.staging)
+                if g.staging_events[i] is not None:
+                    g.staging_events[i].synchronize()          # that staging copy's last upload is done
+                g.staging[i].copy_(torch.from_numpy(g.table))
+                g.table_dev.copy_(g.staging[i], non_blocking=True)
+                if g.table_dev.is_cuda:
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    g.staging_events[i] = ev
                 g.dirty = False
 
     def view(self, cache_id: int) -> Optional[CacheView]:

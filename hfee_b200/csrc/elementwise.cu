@@ -6,28 +6,33 @@
 // ---------------------------------------------------------------- embedding
 // out[i,:] = table[token_i,:] as float32 (the residual stream is float32).
 // Reference: x[i,:] = embed.Row(tokens[i]), hostfog/hfee internal/llm/forward.go:75-77.
+// A negative token id means "the token last sampled on the device for this token's request":
+// it is read from feedback[slot_of_token[i]], so a decode step can be launched before the host
+// has seen the previous step's result.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             const int* __restrict__ slot_of_token, const int* __restrict__ feedback,
                              float* __restrict__ out, int width, int vocab) {
   pdl_wait();
   pdl_launch_dependents();
   int i = blockIdx.x;
   int tok = tokens[i];
+  if (tok < 0 && feedback != nullptr) tok = feedback[slot_of_token[i]];
   bool ok = tok >= 0 && tok < vocab;
   const T* row = table + (long long)(ok ? tok : 0) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x)
     out[(long long)i * width + c] = ok ? to_f32<T>(row[c]) : 0.f;
 }
 
-HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, float* out, int n,
-                        int width, int vocab, cudaStream_t stream) {
+HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, const int* slot_of_token,
+                        const int* feedback, float* out, int n, int width, int vocab, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d vocab=%d", n, width, vocab);
   int threads = width >= 256 ? 256 : 64;
   if (dtype == HFEE_F32)
-    hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, out, width, vocab);
+    hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
   else if (dtype == HFEE_BF16)
-    hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, out, width, vocab);
+    hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
   else
     return hfee_fail(HFEE_ERR_ARG, "embed: unknown dtype %d", dtype);
   return hfee_check_launch("embed");

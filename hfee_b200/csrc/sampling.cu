@@ -12,7 +12,8 @@ constexpr int THREADS = 256;
 
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
-              const double* __restrict__ uniform, int* __restrict__ out) {
+              const double* __restrict__ uniform, int* __restrict__ out, const int* __restrict__ slots,
+              int* __restrict__ feedback) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float s_val[THREADS];
@@ -50,7 +51,10 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   int imax = s_idx[0];
   float T = temperature ? temperature[r] : 0.f;
   if (!(T > 0.f)) {
-    if (tid == 0) out[r] = imax;
+    if (tid == 0) {
+      out[r] = imax;
+      if (feedback) feedback[slots[r]] = imax;
+    }
     return;
   }
 
@@ -76,6 +80,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     }
     if (!found && e == b) pick = imax;
     out[r] = pick;
+    if (feedback) feedback[slots[r]] = pick;
   }
 }
 
@@ -118,7 +123,8 @@ argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int 
   }
 }
 
-__global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out) {
+__global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out,
+                                     const int* __restrict__ slots, int* __restrict__ feedback) {
   pdl_wait();
   pdl_launch_dependents();
   int r = blockIdx.x;
@@ -131,27 +137,29 @@ __global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int 
     if (i < V && (best_i == V || v > best)) { best = v; best_i = i; }   // chunks ascend: ties keep the first
   }
   out[r] = best_i;
+  if (feedback) feedback[slots[r]] = best_i;      // kept on the device for the request's next step
 }
 
 }  // namespace
 
 // scratch: M * chunks * 2 floats.
+// slots/feedback (optional): also store row r's choice in feedback[slots[r]].
 HFEE_API int hfee_argmax(const float* logits, long long ld, int M, int V, int chunks, float* scratch, int* out,
-                         cudaStream_t stream) {
+                         const int* slots, int* feedback, cudaStream_t stream) {
   if (M == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && V > 0 && ld >= V && chunks > 0 && chunks <= 1024 && scratch != nullptr,
                "argmax: bad sizes M=%d V=%d chunks=%d", M, V, chunks);
   HFEE_REQUIRE(M <= 65535, "argmax: too many rows");
   hfee_launch(argmax_stage1_kernel, dim3(dim3((unsigned)chunks, (unsigned)M)), dim3(THREADS), 0, stream, logits, ld, V, chunks, scratch);
-  hfee_launch(argmax_stage2_kernel, dim3(M), dim3(32), 0, stream, scratch, V, chunks, out);
+  hfee_launch(argmax_stage2_kernel, dim3(M), dim3(32), 0, stream, scratch, V, chunks, out, slots, feedback);
   return hfee_check_launch("argmax");
 }
 
 HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const float* temperature,
-                         const double* uniform, int* out, cudaStream_t stream) {
+                         const double* uniform, int* out, const int* slots, int* feedback, cudaStream_t stream) {
   if (M == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && V > 0 && ld >= V, "sample: bad sizes M=%d V=%d ld=%lld", M, V, ld);
   HFEE_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures need uniform numbers");
-  hfee_launch(sample_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, temperature, uniform, out);
+  hfee_launch(sample_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, temperature, uniform, out, slots, feedback);
   return hfee_check_launch("sample");
 }

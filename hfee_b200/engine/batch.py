@@ -31,7 +31,7 @@ class StepBuffers:
 
     def __init__(self, max_tokens: int, max_requests: int, device):
         self.max_tokens, self.max_requests = max_tokens, max_requests
-        self.capacity = 4 * max_tokens + 4 * max_requests + 8
+        self.capacity = 5 * max_tokens + 4 * max_requests + 8
         self.device = torch.device(device)
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=self.device)
         pin = self.device.type == "cuda"
@@ -59,7 +59,7 @@ class Step:
     """What the parts see of a step.
 
     Device int32 tensors: ``token_ids[n]``, ``positions[n]``, ``slot_of_token[n]``,
-    ``logit_rows[n_logits]`` (flat token indices), ``cu_tokens[r+1]``, ``slots[r]``,
+    ``logit_rows[n_logits]`` (flat token indices), ``logit_slots[n_logits]``, ``cu_tokens[r+1]``, ``slots[r]``,
     ``context_before[r]``, ``context_after[r]``.  Host: ``requests`` = list of
     (slot, first position, token count) in batch order; ``memo`` for work that parts
     share within the step (rotary tables); ``max_context`` = longest context after
@@ -74,10 +74,10 @@ class Step:
             raise ValueError(f"step of {n} tokens exceeds the batch limit of {buffers.max_tokens}")
         if r > buffers.max_requests:
             raise ValueError(f"step of {r} requests exceeds the limit of {buffers.max_requests}")
-        packed = np.empty(3 * n + m + 4 * r + 1, dtype=np.int32)
+        packed = np.empty(3 * n + 2 * m + 4 * r + 1, dtype=np.int32)
         tok, pos, slot = packed[0:n], packed[n:2 * n], packed[2 * n:3 * n]
-        rows = packed[3 * n:3 * n + m]
-        o = 3 * n + m
+        rows, row_slots = packed[3 * n:3 * n + m], packed[3 * n + m:3 * n + 2 * m]
+        o = 3 * n + 2 * m
         cu, slots = packed[o:o + r + 1], packed[o + r + 1:o + 2 * r + 1]
         before, after = packed[o + 2 * r + 1:o + 3 * r + 1], packed[o + 3 * r + 1:o + 4 * r + 1]
         self.requests: List[Tuple[int, int, int]] = []
@@ -93,6 +93,7 @@ class Step:
                 if not 0 <= idx < k:
                     raise ValueError(f"entry {j}: wanted index {idx} is outside its {k} tokens")
                 rows[w] = at + idx
+                row_slots[w] = e.slot
                 w += 1
             self.requests.append((e.slot, start, k))
             at += k
@@ -103,6 +104,8 @@ class Step:
         d = buffers.dev
         self.token_ids, self.positions, self.slot_of_token = d[0:n], d[n:2 * n], d[2 * n:3 * n]
         self.logit_rows = d[3 * n:3 * n + m]
+        self.logit_slots = d[3 * n + m:3 * n + 2 * m]       # request slot of each wanted row
+        self.feedback = None        # int32 per slot: tokens sampled on the device (set by the runner)
         self.cu_tokens, self.slots = d[o:o + r + 1], d[o + r + 1:o + 2 * r + 1]
         self.context_before, self.context_after = d[o + 2 * r + 1:o + 3 * r + 1], d[o + 3 * r + 1:o + 4 * r + 1]
         self.max_context = max((s + k for _, s, k in self.requests), default=0)

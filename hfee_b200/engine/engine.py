@@ -17,7 +17,7 @@ from ..kernels import ops
 from ..sampling import BatchSampler, SamplingOptions
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import FinishReason, Request, RequestStats, Scheduler
+from .scheduler import DEVICE_TOKEN, FinishReason, Request, RequestStats, Scheduler
 
 
 @dataclass
@@ -60,6 +60,7 @@ class Engine:
         self.sampler = BatchSampler(self.runner.device, engine.max_requests)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self.tokenizer = _load_tokenizer(model_dir)
+        self.pipeline = True          # overlap host work with the GPU where the sampling options allow it
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._next_id = 0
@@ -103,6 +104,34 @@ class Engine:
             requests.append(req)
         emitted = [0] * len(requests)
         cut = {}                     # request index -> text cut at its stop string
+
+        def emit() -> None:
+            if on_token is None:
+                return
+            for i, r in enumerate(requests):
+                while emitted[i] < len(r.output) and r.output[emitted[i]] != DEVICE_TOKEN:
+                    on_token(i, r.output[emitted[i]])
+                    emitted[i] += 1
+
+        # When every request samples on the device and nothing needs text, steps are pipelined:
+        # the sampled tokens stay on the device for the next step and the host reads them one step
+        # late, so planning and launching overlap the GPU's work.
+        if self.pipeline and all(o.device_only and not o.stop for o in options):
+            inflight = None
+            while not sched.idle or inflight is not None:
+                launched = self.launch_step(sched) if not sched.idle else None
+                if inflight is not None:
+                    pending, handle = inflight
+                    if handle is not None:
+                        tokens = self.sampler.fetch(handle)
+                        self.d2h_bytes += 4 * len(tokens)
+                        sched.resolve(pending, tokens)
+                inflight = launched
+                emit()
+                sched.pop_finished()
+            ops.check_status()
+            return [GenerationResult(list(r.output), self.decode(r.output), r.stats) for r in requests]
+
         while not sched.idle:
             self.run_step(sched)
             for i, r in enumerate(requests):       # stop strings (text.go:41-78), when text is available
@@ -112,15 +141,29 @@ class Engine:
                     if hits:
                         cut[i] = text[:min(hits)]
                         sched.finish(r, FinishReason.STOP)
-            if on_token is not None:
-                for i, r in enumerate(requests):
-                    while emitted[i] < len(r.output):
-                        on_token(i, r.output[emitted[i]])
-                        emitted[i] += 1
+            emit()
             sched.pop_finished()
         ops.check_status()
         return [GenerationResult(list(r.output), cut.get(i, self.decode(r.output)), r.stats)
                 for i, r in enumerate(requests)]
+
+    def launch_step(self, sched: Scheduler):
+        """Plan and launch one step without waiting for its result.  Returns (pending, handle) for
+        ``Scheduler.resolve`` / ``BatchSampler.fetch``, or None if nothing could run."""
+        plan = sched.plan()
+        if not plan:
+            return None
+        entries = [StepEntry(e.request.slot, e.tokens, (len(e.tokens) - 1,) if e.wants_logits else ())
+                   for e in plan]
+        logits = self.runner.step(entries)
+        step = self.runner.last_step
+        self.h2d_bytes += step.h2d_bytes
+        handle = None
+        if logits is not None:
+            who = [e.request for e in plan if e.wants_logits]
+            handle = self.sampler.launch(logits, [r.options for r in who], [r.seed for r in who],
+                                         [r.draws for r in who], step.logit_slots, self.runner.feedback)
+        return sched.update_provisional(plan), handle
 
     def run_step(self, sched: Scheduler) -> int:
         """Plan, run and account for one step; returns the number of tokens it ran."""

@@ -19,6 +19,7 @@ from ..weights import Checkpoint
 from .batch import Step, StepBuffers, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+DEVICE_TOKEN = -1        # as a single-token entry: "the token the device sampled last for this request"
 
 
 class ModelRunner:
@@ -38,6 +39,9 @@ class ModelRunner:
                                   e.max_context, self.rt.dtype, self.device)
         self.buffers = StepBuffers(e.max_batch_tokens, e.max_requests, self.device)
         self.vocab = self.spec.vocab
+        # the token last sampled on the device for each request slot; a step may name it with
+        # the token id DEVICE_TOKEN instead of a value the host has not read back yet
+        self.feedback = torch.zeros(e.max_requests, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         # decode-only steps are captured in a CUDA graph per batch size: first sight runs
         # eagerly (and makes every scratch buffer), second sight captures, later ones replay
@@ -71,6 +75,8 @@ class ModelRunner:
                 raise ValueError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
             lo, hi = min(e.tokens), max(e.tokens)
+            if lo == DEVICE_TOKEN and len(e.tokens) == 1:
+                lo = 0
             if lo < 0 or hi >= self.vocab:
                 raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {self.vocab}")
             if cache.length[e.slot] + len(e.tokens) > cache.max_context:
@@ -85,6 +91,7 @@ class ModelRunner:
             cache.reserve(e.slot, cache.length[e.slot] + len(e.tokens))
         cache.sync()
         step = Step(entries, cache.length, self.buffers)
+        step.feedback = self.feedback
         if (self.engine.use_cuda_graphs and self.device.type == "cuda" and step.decode_only
                 and all(tuple(e.want) == (0,) for e in entries)):
             logits = self._graphed_forward(step)

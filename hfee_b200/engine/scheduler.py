@@ -25,6 +25,9 @@ from ..sampling.sampler import fresh_seed
 from .batch import StepEntry
 
 
+DEVICE_TOKEN = -1      # placeholder for a token that was sampled on the device and not read back yet
+
+
 class FinishReason:
     STOP = "stop"          # an end token was sampled (or a stop string matched)
     LENGTH = "length"      # num_predict reached, the context is full, or the cache cannot hold it
@@ -144,6 +147,8 @@ class Scheduler:
             if self._pages_for(first) + promised > self.cache.free_pages() and self.running:
                 break          # wait for pages; with nothing running, _build shrinks the portion instead
             self.waiting.popleft()
+            if req.stats.preemptions and not req.decoding:
+                req.feed = req.prompt + req.output        # recompute everything it has so far
             req.slot = self.cache.open()
             req.order = self._admissions
             self._admissions += 1
@@ -202,8 +207,8 @@ class Scheduler:
         self.cache.close(req.slot)
         self.running.remove(req)
         req.slot = None
-        req.feed = req.prompt + req.output          # recompute everything when re-admitted
-        req.decoding = False
+        req.feed = req.prompt + req.output          # recompute everything when re-admitted (rebuilt at admission,
+        req.decoding = False                        # when placeholders in the output have been resolved)
         req.stats.preemptions += 1
         self.preemptions += 1
         self.waiting.appendleft(req)
@@ -236,7 +241,57 @@ class Scheduler:
             else:
                 req.feed = [tok]
 
+    # ------------------------------------------------------------------ results, one step late
+    def update_provisional(self, entries: Sequence[PlannedEntry]) -> List[Tuple[Request, int]]:
+        """Account for a step that was launched but whose sampled tokens stay on the device for
+        now: each request whose logits were computed gets the placeholder ``DEVICE_TOKEN`` as its
+        new output and next input.  Returns (request, output index) pairs in the order of the
+        step's logits rows, for :meth:`resolve`."""
+        pending: List[Tuple[Request, int]] = []
+        now = self.clock()
+        for e in entries:
+            req = e.request
+            req.feed = req.feed[len(e.tokens):]
+            if not e.wants_logits:
+                continue
+            if not req.decoding:
+                req.decoding = True
+                if not req.eval_started:
+                    req.stats.prompt_seconds = now - req.started
+                    req.eval_started = now
+            req.draws += 1
+            req.output.append(DEVICE_TOKEN)
+            req.stats.eval_tokens += 1
+            pending.append((req, len(req.output) - 1))
+            if 0 <= req.options.num_predict <= req.stats.eval_tokens:
+                self._finish(req, FinishReason.LENGTH)
+            else:
+                req.feed = [DEVICE_TOKEN]
+        return pending
+
+    def resolve(self, pending: Sequence[Tuple[Request, int]], tokens: Sequence[int]) -> None:
+        """Fill in the tokens of an earlier :meth:`update_provisional`.  An end token found now
+        ends its request at that point: it and whatever was provisionally produced after it are
+        dropped (the reference does not emit or count the end token, runner.go:288-291)."""
+        for (req, idx), tok in zip(pending, tokens):
+            if idx >= len(req.output):
+                continue                                  # cut off by an end token found earlier
+            tok = int(tok)
+            if tok in self.eos:
+                dropped = len(req.output) - idx
+                del req.output[idx:]
+                req.stats.eval_tokens -= dropped
+                req.feed = []
+                if req.finished:
+                    req.finished = req.stats.done_reason = FinishReason.STOP
+                else:
+                    self._finish(req, FinishReason.STOP)
+            else:
+                req.output[idx] = tok
+
     def _finish(self, req: Request, reason: str) -> None:
+        if req in self.waiting:
+            self.waiting.remove(req)
         if req.slot is not None:
             self.cache.close(req.slot)
             req.slot = None

@@ -26,7 +26,7 @@ _L = ctypes.c_longlong
 _F = ctypes.c_float
 
 _SIGNATURES = {
-    "hfee_embed": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "hfee_embed": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
     "hfee_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "hfee_rope_table": [_P, _P, _P, _I, _I, _P],
     "hfee_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -39,8 +39,8 @@ _SIGNATURES = {
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
-    "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P],
+    "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P],
 }
 
 
@@ -126,14 +126,18 @@ def _i32(t: Optional[torch.Tensor], what: str) -> None:
 
 
 # ----------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[i,:] = table[tokens[i],:] widened to float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, slot_of_token: Optional[torch.Tensor] = None,
+          feedback: Optional[torch.Tensor] = None) -> None:
+    """out[i,:] = table[tokens[i],:] widened to float32.  With ``feedback`` (int32 per request slot)
+    a negative token id stands for ``feedback[slot_of_token[i]]``: the token last sampled on the
+    device for that request."""
     lib = library()
-    _i32(tokens, "embed tokens")
+    _i32(tokens, "embed tokens"); _i32(slot_of_token, "slot_of_token"); _i32(feedback, "feedback")
     assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
+    assert feedback is None or slot_of_token is not None
     n, width = out.shape
-    _check(lib.hfee_embed(table.data_ptr(), _dt(table), tokens.data_ptr(), out.data_ptr(), n, width,
-                          table.shape[0], _stream()), lib)
+    _check(lib.hfee_embed(table.data_ptr(), _dt(table), tokens.data_ptr(), _ptr(slot_of_token), _ptr(feedback),
+                          out.data_ptr(), n, width, table.shape[0], _stream()), lib)
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -461,27 +465,35 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           uniform: Optional[torch.Tensor] = None) -> None:
+           uniform: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+           feedback: Optional[torch.Tensor] = None) -> None:
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or no temperatures are given),
-    else a draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1)."""
+    else a draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1).  With ``slots``
+    and ``feedback`` the choice is also stored in ``feedback[slots[r]]``."""
     lib = library()
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.is_contiguous()
+    _i32(slots, "slots"); _i32(feedback, "feedback")
+    assert (slots is None) == (feedback is None)
     m, v = logits.shape
     if temperature is not None:
         assert temperature.dtype == torch.float32 and uniform.dtype == torch.float64
     _check(lib.hfee_sample(logits.data_ptr(), _rows(logits, "logits"), m, v, _ptr(temperature), _ptr(uniform),
-                           out.data_ptr(), _stream()), lib)
+                           out.data_ptr(), _ptr(slots), _ptr(feedback), _stream()), lib)
 
 
 ARGMAX_CHUNKS = 64
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor) -> None:
-    """out[r] = index of the first maximum of logits[r]; ``scratch`` holds rows * ARGMAX_CHUNKS * 2 floats."""
+def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots: Optional[torch.Tensor] = None,
+           feedback: Optional[torch.Tensor] = None) -> None:
+    """out[r] = index of the first maximum of logits[r]; ``scratch`` holds rows * ARGMAX_CHUNKS * 2
+    floats.  With ``slots`` and ``feedback`` the choice is also stored in ``feedback[slots[r]]``."""
     lib = library()
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and scratch.dtype == torch.float32
+    _i32(slots, "slots"); _i32(feedback, "feedback")
+    assert (slots is None) == (feedback is None)
     m, v = logits.shape
     assert scratch.numel() >= m * ARGMAX_CHUNKS * 2
     _check(lib.hfee_argmax(logits.data_ptr(), _rows(logits, "logits"), m, v, ARGMAX_CHUNKS, scratch.data_ptr(),
-                           out.data_ptr(), _stream()), lib)
+                           out.data_ptr(), _ptr(slots), _ptr(feedback), _stream()), lib)
     count_launches(1)

@@ -25,7 +25,7 @@ class TokenEmbedding(Part):
         self.table = tensors["table"]
 
     def forward(self, step: Any, residual: torch.Tensor) -> None:
-        ops.embed(self.table, step.token_ids, residual)
+        ops.embed(self.table, step.token_ids, residual, step.slot_of_token, getattr(step, "feedback", None))
 
 
 class LinearHead(Part):

@@ -105,6 +105,10 @@ class BatchSampler:
         self.temp = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
         self.unif = torch.zeros(max_rows, dtype=torch.float64, device=self.device)
         self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        # two sets of result buffers so that a step's choice can be read back while the next is made
+        self.outs = [torch.zeros(max_rows, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self.out_hosts = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.turn = 0
         self.argmax_scratch = torch.zeros(max_rows * ops.ARGMAX_CHUNKS * 2, dtype=torch.float32, device=self.device)
 
     def sample(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
@@ -128,3 +132,34 @@ class BatchSampler:
                 row = logits[i].cpu().numpy()
                 tokens[i] = sample_host(row, histories[i], o, us[i])
         return tokens
+
+    # -- pipelined use: launch now, read the result one step later -------------------------------
+    def launch(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
+               draws: Sequence[int], slots: torch.Tensor, feedback: torch.Tensor):
+        """Start choosing a token for each row on the device (options must all be ``device_only``):
+        the choices go to ``feedback[slots[r]]`` for the next step and, asynchronously, to pinned
+        host memory.  Returns a handle for :meth:`fetch`."""
+        m = logits.shape[0]
+        assert m == len(options) <= self.max_rows and all(o.device_only for o in options)
+        b = self.turn
+        self.turn ^= 1
+        out = self.outs[b][:m]
+        if all(o.temperature <= 0 for o in options):
+            ops.argmax(logits, out, self.argmax_scratch, slots, feedback)
+        else:
+            us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
+            self.temp[:m].copy_(torch.tensor([o.temperature for o in options], dtype=torch.float32))
+            self.unif[:m].copy_(torch.tensor(us, dtype=torch.float64))
+            ops.sample(logits, out, self.temp[:m], self.unif[:m], slots, feedback)
+        self.out_hosts[b][:m].copy_(out, non_blocking=True)
+        event = torch.cuda.Event() if self.device.type == "cuda" else None
+        if event is not None:
+            event.record()
+        return b, m, event
+
+    def fetch(self, handle) -> List[int]:
+        """The tokens of a :meth:`launch` (waits for that step, not for later ones)."""
+        b, m, event = handle
+        if event is not None:
+            event.synchronize()
+        return self.out_hosts[b][:m].tolist()

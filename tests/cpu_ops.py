@@ -10,8 +10,11 @@ import math
 import torch
 
 
-def embed(table, tokens, out):
-    out.copy_(table[tokens.long()].float())
+def embed(table, tokens, out, slot_of_token=None, feedback=None):
+    tok = tokens.long()
+    if feedback is not None:
+        tok = torch.where(tok < 0, feedback[slot_of_token.long()].long(), tok)
+    out.copy_(table[tok].float())
 
 
 def rmsnorm(x, weight, out, eps, rows=None, add_unit=False):
@@ -94,7 +97,13 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
             out[i, h * head_dim:(h + 1) * head_dim] = (p @ v[:, h // group, :]).to(out.dtype)
 
 
-def sample(logits, out, temperature=None, uniform=None):
+def sample(logits, out, temperature=None, uniform=None, slots=None, feedback=None):
+    _sample(logits, out, temperature, uniform)
+    if feedback is not None:
+        feedback[slots.long()] = out
+
+
+def _sample(logits, out, temperature=None, uniform=None):
     for r in range(logits.shape[0]):
         t = float(temperature[r]) if temperature is not None else 0.0
         if t <= 0:
@@ -113,8 +122,10 @@ def linear_swiglu_normed(inp, w_gate_up, out, granule, scratch):
     linear_swiglu(inp if isinstance(inp, torch.Tensor) else inp.tensor(), w_gate_up, out, granule, scratch)
 
 
-def argmax(logits, out, scratch):
+def argmax(logits, out, scratch, slots=None, feedback=None):
     out.copy_(torch.argmax(logits, dim=1).to(torch.int32))
+    if feedback is not None:
+        feedback[slots.long()] = out
 
 
 ALL = ("argmax", "linear_normed", "linear_swiglu_normed", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_swiglu",

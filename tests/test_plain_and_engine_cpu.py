@@ -94,3 +94,38 @@ def test_bfloat16_weight_layouts_on_cpu(tiny_dirs, cpu_ops):
     out = r.step([StepEntry(r.open(), toks, list(range(len(toks))))]).numpy()
     assert r.model.blocks[0].feed_forward.granule == 4
     assert float(np.max(np.abs(out - ref)) / np.max(np.abs(ref))) < 2e-2
+
+
+@pytest.mark.parametrize("pipeline", [False, True])
+def test_generate_on_cpu_doubles_pipelined_and_not(tiny_dirs, cpu_ops, pipeline):
+    """Engine.generate end to end over the CPU doubles: greedy tokens equal the plain
+    implementation's with and without pipelining, with an end token, and under a cache so small
+    that requests are preempted and recomputed."""
+    import json, os, shutil, tempfile
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs["A"])
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (20, 25, 30)]
+    want = [plain.greedy_generate(cfg, w, p, 12) for p in prompts]
+    eng = Engine(tiny_dirs["A"], dtype="float32", page_size=16, max_requests=3, max_context=128,
+                 max_batch_tokens=64, max_cache_tokens=6 * 16, device="cpu")
+    eng.pipeline = pipeline
+    seen = [[] for _ in prompts]
+    res = eng.generate(prompts, SamplingOptions.greedy(num_predict=12), on_token=lambda i, t: seen[i].append(t))
+    assert [r.token_ids for r in res] == want and seen == want
+    assert sum(r.stats.preemptions for r in res) > 0
+    assert eng.runner.cache.free_pages() == 6 and eng.runner.cache.free_slots() == 3
+    # an end token: generation stops before it
+    d = tempfile.mkdtemp()
+    shutil.copytree(tiny_dirs["A"], d, dirs_exist_ok=True)
+    c = json.load(open(os.path.join(d, "config.json")))
+    c["eos_token_id"] = want[0][5]
+    json.dump(c, open(os.path.join(d, "config.json"), "w"))
+    eng2 = Engine(d, dtype="float32", page_size=16, max_requests=3, max_context=128, max_batch_tokens=64, device="cpu")
+    eng2.pipeline = pipeline
+    res2 = eng2.generate(prompts, SamplingOptions.greedy(num_predict=12))
+    for r, wnt in zip(res2, want):
+        cut = wnt.index(want[0][5]) if want[0][5] in wnt else len(wnt)
+        assert r.token_ids == wnt[:cut]
+        assert r.stats.done_reason == ("stop" if cut < len(wnt) else "length") and r.stats.eval_tokens == cut
+    shutil.rmtree(d)

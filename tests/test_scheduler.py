@@ -164,3 +164,35 @@ def test_abort_frees_and_reports():
     s.add(c)
     s.abort(c)
     assert c.finished == FinishReason.ABORT and [r.id for r in s.pop_finished()] == ["a", "c"]
+
+
+def test_provisional_updates_resolve_one_step_late():
+    from hfee_b200.engine.scheduler import DEVICE_TOKEN
+    cache, s = make(eos=(7,))
+    a, b, c = req("a", 3, num_predict=3), req("b", 3), req("c", 3)
+    for r in (a, b, c):
+        s.add(r)
+
+    def launch():
+        plan = s.plan()
+        for e in plan:
+            new = cache.length[e.request.slot] + len(e.tokens)
+            cache.reserve(e.request.slot, new)
+            cache.commit(e.request.slot, new)
+        return s.update_provisional(plan)
+
+    p0 = launch()                                  # prompts; tokens unknown yet
+    assert [r.id for r, _ in p0] == ["a", "b", "c"] and a.output == [DEVICE_TOKEN] and a.feed == [DEVICE_TOKEN]
+    p1 = launch()                                  # launched before p0 is known: inputs are placeholders
+    assert all(e == [DEVICE_TOKEN] for e in (a.feed, b.feed, c.feed))
+    s.resolve(p0, [50, 7, 51])                     # b's first token was an end token
+    assert a.output == [50, DEVICE_TOKEN] and b.output == [] and b.finished == FinishReason.STOP
+    assert b.stats.eval_tokens == 0 and c.output == [51, DEVICE_TOKEN]
+    p2 = launch()                                  # b is gone; a reaches num_predict = 3 and ends provisionally
+    assert [r.id for r, _ in p2] == ["a", "c"] and a.finished == FinishReason.LENGTH
+    s.resolve(p1, [60, 61, 62])                    # b's row is ignored: its output was cut
+    assert a.output == [50, 60, DEVICE_TOKEN] and b.output == [] and c.output == [51, 62, DEVICE_TOKEN]
+    s.resolve(p2, [7, 63])                         # a's third token turns out to be an end token
+    assert a.output == [50, 60] and a.finished == FinishReason.STOP and a.stats.eval_tokens == 2
+    assert c.output == [51, 62, 63]
+    cache.check_invariants()
