@@ -62,6 +62,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (2 ulp; 2^-inf = 0), as flash-attention kernels use it.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -114,6 +120,13 @@ attention_mma_kernel(AttnParams p) {
   // The batch layout and the block table come from the host, not from the previous kernel: they
   // were read (and the table rows of this CTA's blocks pulled into cache) while that kernel may
   // still be running.  Queries and this step's keys/values are its output: wait for it now.
+  // lowest and highest position among this warp's valid rows (warp-uniform), to tell which
+  // blocks need no mask at all; a warp without valid rows masks everything
+  int row_pos_min = pos_first + wrow / p.group;
+  int row_pos_max = pos_first + min(wrow + 15, rows_used - 1) / p.group;
+  if (wrow >= rows_used) { row_pos_min = -1; row_pos_max = -1; }
+  else if (wrow + 15 >= rows_used) row_pos_min = -1;          // padding rows in the tile: keep masking
+
   if (b_lo <= b_hi && tid <= b_hi - b_lo) {
     int warm = p.cache.block_table[(long long)slot * p.cache.max_pages + (b_lo + tid) * BLOCK_N / p.cache.page_size];
     asm volatile("" ::"r"(warm));
@@ -210,26 +223,36 @@ attention_mma_kernel(AttnParams p) {
       }
     }
 
-    // ---- mask, scale to log2 units, online softmax
+    // ---- mask (only in blocks that reach past a row's position or below its window), online
+    // softmax on the raw scores: p = 2^(s*c - m*c) with c = scale*log2(e) folded into one FMA
+    const float c_log2 = p.scale_log2;
+    const int key0 = b * BLOCK_N + wkey;                       // first key this warp visits in the block
+    const int row_lo = min(row_pos_min, row_pos_max), row_hi = row_pos_max;
+    const bool need_mask = key0 + WKEYS - 1 > row_lo || (p.window > 0 && key0 <= row_hi - p.window);
     float m_new[2] = {m_run[0], m_run[1]};
+    if (need_mask) {
+#pragma unroll
+      for (int nt = 0; nt < WKEYS / 8; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int h = j >> 1;
+          int key = key0 + nt * 8 + 2 * c + (j & 1);
+          bool ok = key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
+          if (!ok) s[nt][j] = -INFINITY;
+        }
+    }
 #pragma unroll
     for (int nt = 0; nt < WKEYS / 8; ++nt)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int h = j >> 1;
-        int key = b * BLOCK_N + wkey + nt * 8 + 2 * c + (j & 1);
-        bool ok = key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
-        float v = ok ? s[nt][j] * p.scale_log2 : -INFINITY;
-        s[nt][j] = v;
-        m_new[h] = fmaxf(m_new[h], v);
-      }
-    float alpha[2], m_use[2];
+      for (int j = 0; j < 4; ++j) m_new[j >> 1] = fmaxf(m_new[j >> 1], s[nt][j]);
+    float alpha[2], neg_mc[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
-      alpha[h] = exp2f(m_run[h] - m_use[h]);
+      float m_use = m_new[h] == -INFINITY ? 0.f : m_new[h];
+      alpha[h] = fast_exp2((m_run[h] - m_use) * c_log2);       // 0 while the row has seen no key
+      neg_mc[h] = -m_use * c_log2;
       m_run[h] = m_new[h];
     }
     float l_add[2] = {0.f, 0.f};
@@ -238,7 +261,7 @@ attention_mma_kernel(AttnParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         int h = j >> 1;
-        float e = exp2f(s[nt][j] - m_use[h]);
+        float e = fast_exp2(fmaf(s[nt][j], c_log2, neg_mc[h]));
         s[nt][j] = e;
         l_add[h] += e;
       }
@@ -289,7 +312,8 @@ attention_mma_kernel(AttnParams p) {
 #pragma unroll
       for (int i = 0; i < HD / 8; ++i)
         *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
-      if (c == 0) { mm[warp * 16 + row] = m_run[h]; ml[warp * 16 + row] = l_run[h]; }
+      // running maxima are in raw score units; merges and partial results use log2 units
+      if (c == 0) { mm[warp * 16 + row] = m_run[h] * p.scale_log2; ml[warp * 16 + row] = l_run[h]; }
     }
     __syncthreads();
     for (int idx = tid; idx < rows_used * (HD / 2); idx += THREADS) {
@@ -338,7 +362,7 @@ attention_mma_kernel(AttnParams p) {
       for (int i = 0; i < HD / 8; ++i)
         *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
       if (c == 0) {
-        p.part_ml[idx * 2] = m_run[h];
+        p.part_ml[idx * 2] = m_run[h] * p.scale_log2;
         p.part_ml[idx * 2 + 1] = l_run[h];
       }
     }

@@ -195,10 +195,11 @@ def _register_toy():
         inner: int
         vocab: int
         eps: float
+        window: int
 
         @classmethod
         def from_dict(cls, d):
-            return cls(d["width"], d["heads"], d["head_dim"], d["inner"], d["vocab_size"], d["eps"])
+            return cls(d["width"], d["heads"], d["head_dim"], d["inner"], d["vocab_size"], d["eps"], d["window"])
 
     def toy_spec(c):
         pos = PartSpec("rotary", head_dim=c.head_dim, rope_dim=c.head_dim // 2, theta=1000.0, scaling=None, pairing="half")
@@ -216,10 +217,13 @@ def _register_toy():
             names.update({f"mixer.{k}": p + k for k in mixer_names})
             return LayerSpec(block=block, mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm, names=names)
 
-        layers = (layer(0, attn, "qkvo"), layer(1, mean, "w"), layer(2, attn, "qkvo"))
+        local = attn.replace(window=c.window, position=PartSpec("none"))
+        layers = (layer(0, attn, "qkvo"), layer(1, mean, "w"), layer(2, attn, "qkvo"), layer(3, local, "qkvo"))
         # layer 0 (attention), layer 1 (running mean), layer 1 again with a state of its own,
-        # then layer 2, which projects only queries and attends over the cache layer 0 wrote
-        schedule = (RunSpec(0, cache=0), RunSpec(1, cache=1), RunSpec(1, cache=2), RunSpec(2, cache=0, writes_cache=False))
+        # layer 2, which projects only queries and attends over the cache layer 0 wrote, and
+        # layer 3: attention over a window of its own cache, without position encoding
+        schedule = (RunSpec(0, cache=0), RunSpec(1, cache=1), RunSpec(1, cache=2), RunSpec(2, cache=0, writes_cache=False),
+                    RunSpec(3, cache=3))
         return ModelSpec(width=c.width, vocab=c.vocab, embedding=PartSpec("token", vocab=c.vocab, width=c.width),
                          layers=layers, schedule=schedule, final_norm=norm,
                          head=PartSpec("linear", vocab=c.vocab, width=c.width, tied=True),
@@ -229,7 +233,7 @@ def _register_toy():
 
 
 TOY = {"architectures": ["ToyStateForCausalLM"], "width": 80, "heads": 5, "head_dim": 32, "inner": 116,
-       "vocab_size": 211, "eps": 1e-5}
+       "vocab_size": 211, "eps": 1e-5, "window": 21}
 
 
 def toy_plain_forward(w, tokens, bf16):
@@ -261,6 +265,10 @@ def toy_plain_forward(w, tokens, bf16):
     xb = plain.rms_norm(x, w["toy.2.n1"], c["eps"])
     q2 = rope_partial(plain.linear(xb, f(w["toy.2.q"])), 5)
     x = ffn(x + plain.linear(plain.attention(q2, k0, v0, 5, 1, 32), f(w["toy.2.o"])), "toy.2.")
+    xb = plain.rms_norm(x, w["toy.3.n1"], c["eps"])                      # windowed, no position encoding
+    att = plain.attention(plain.linear(xb, f(w["toy.3.q"])), plain.linear(xb, f(w["toy.3.k"])),
+                          plain.linear(xb, f(w["toy.3.v"])), 5, 1, 32, window=c["window"])
+    x = ffn(x + plain.linear(att, f(w["toy.3.o"])), "toy.3.")
     return plain.linear(plain.rms_norm(x, w["toy.norm"], c["eps"]), f(w["toy.embed"]))
 
 
@@ -280,8 +288,17 @@ def test_toy_architecture_with_state_runs_through_the_engine(tmp_path, dtype):
     runner = ModelRunner(d, e)
     needs = runner.model.cache_needs()
     assert needs[0] == PagedKV(1, 32, None) and needs[1] == needs[2] == FixedState((80,), "float32")
-    assert len(runner.cache.paged) == 1 and len(runner.cache.states) == 1
+    assert needs[3] == PagedKV(1, 32, 21)
+    assert len(runner.cache.paged) == 2 and len(runner.cache.states) == 1
+    windowed = [g for g in runner.cache.paged if g.need.window][0]
     for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(7, 2, 16, 3, 2, 33)), ru.mixed(seqs, live=3, seed=1)):
         got = ru.run_in_process(runner, steps)
         for i in range(len(seqs)):
             assert ru.rel_err(got[i], refs[i]) < TOL[dtype], f"request {i}"
+    # the windowed group gave pages back while requests were still running: a request of 70 tokens
+    # never held more than ceil((21 + longest portion) / 16) + 1 of them
+    s = runner.open()
+    for t in range(0, 70, 2):
+        runner.step([__import__("hfee_b200").StepEntry(s, seqs[3][t:t + 2], [])])
+        assert int((windowed.table[s] >= 0).sum()) <= 3
+    runner.close(s)
