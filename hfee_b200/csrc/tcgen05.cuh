@@ -10,7 +10,7 @@
 namespace tc {
 
 constexpr int BK = 64;                        // K elements per pipeline stage: one 128-byte swizzle row of bf16
-constexpr uint32_t WAIT_LIMIT = 4u << 20;     // polls (with back-off sleeps) before a wait gives up: ~ a second
+constexpr uint32_t WAIT_LIMIT = 1u << 18;     // suspended attempts before a wait gives up: about a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -23,23 +23,24 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+// One attempt: the thread is suspended by the hardware until the phase with `parity` completes or
+// a time limit (hinted in nanoseconds) passes; returns whether the phase completed.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(8000u) : "memory");
   return ok != 0;
 }
-// Waits for the phase with `parity` to complete; false if the wait ran out or the CTA is aborting.
+// Waits for the phase with `parity` to complete; false if the wait ran out (WAIT_LIMIT attempts of
+// at most a few microseconds each: about a second) or the CTA is aborting.  A suspended thread
+// issues no instructions, so waiting warps do not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if (*abort_flag) return false;
-    }
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   return false;

@@ -142,10 +142,13 @@ def main(argv=None) -> int:
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--tc-attention", action="store_true", help="attention_prefill: the tcgen05 kernel (the default)")
+    ap.add_argument("--no-tc-attention", action="store_true", help="attention_prefill: the mma.sync kernel")
     ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (no host launch cost)")
     args = ap.parse_args(argv)
     global GRAPH
     GRAPH = args.graph
+    ops.USE_TC_ATTENTION = args.tc_attention or not args.no_tc_attention
     torch.manual_seed(0)
     if args.kernel.startswith("gemm"):
         res = _gemm(args, args.kernel)

@@ -36,6 +36,8 @@ _SIGNATURES = {
     "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "hfee_gemm_skinny": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _P],
     "hfee_gemm_skinny_splits": [_I, _I, _I, _L],
+    "hfee_attention_tc": [_P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "hfee_attention_tc_supports": [_I, _I, _I, _I],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -59,6 +61,7 @@ def library() -> ctypes.CDLL:
     lib.hfee_last_error.restype = ctypes.c_char_p
     lib.hfee_device_is_sm100.restype = _I
     lib.hfee_gemm_skinny_splits.restype = _I
+    lib.hfee_attention_tc_supports.restype = _I
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -244,7 +247,7 @@ def check_status() -> None:
     """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
     if _STATUS is not None and int(_STATUS.item()) != 0:
         _STATUS.zero_()
-        raise KernelLibraryError("a tensor-core GEMM gave up waiting on a barrier; its output is invalid")
+        raise KernelLibraryError("a tcgen05 kernel gave up waiting on a barrier; its output is invalid")
 
 
 def _tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -443,6 +446,31 @@ def attention_mma(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, c
         count_launches(1)
 
 
+USE_TC_ATTENTION = True
+
+
+def attention_tc(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, context_before, out, n_tokens,
+                 requests, max_new, heads, kv_heads, head_dim, scale, window=0) -> None:
+    """Flash attention for prompt portions on tcgen05 (S and O accumulators in tensor memory, TMA-fed
+    pages, one softmax thread per query row).  bfloat16, head size 64, pages of at least 64 tokens."""
+    lib = library()
+    for t, what in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (slots, "slots"),
+                    (context_before, "context_before")):
+        _i32(t, what)
+    assert q.dtype == k_pool.dtype == out.dtype == torch.bfloat16
+    assert k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    _check(lib.hfee_attention_tc(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0],
+                                 block_table.data_ptr(), block_table.shape[1], page_size, cu_tokens.data_ptr(),
+                                 slots.data_ptr(), context_before.data_ptr(), out.data_ptr(),
+                                 _rows(out, "attention out"), n_tokens, requests, max_new, heads, kv_heads, head_dim,
+                                 float(scale), int(window or 0), _status().data_ptr(), _stream()), lib)
+
+
+def attention_tc_supports(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return bool(library().hfee_attention_tc_supports(heads, kv_heads, head_dim, page_size))
+
+
 def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
                     head_dim, scale, window=0, step=None, scratch=None) -> None:
     """Attention over the cache, choosing the kernel for the dtype and the batch.  ``step`` gives
@@ -451,6 +479,11 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
     group = heads // kv_heads
     if (step is not None and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
             and group <= 64 and _rows(q, "q") % 8 == 0):
+        if (USE_TC_ATTENTION and step.max_new * group > 16 and _rows(out, "out") % 8 == 0
+                and attention_tc_supports(heads, kv_heads, head_dim, page_size)):
+            attention_tc(q, k_pool, v_pool, block_table, page_size, step.cu_tokens, step.slots, step.context_before,
+                         out, step.n, step.r, step.max_new, heads, kv_heads, head_dim, scale, window)
+            return
         splits = 1
         if step.max_new * group <= 16 and scratch is not None:
             splits = getattr(step, "attention_splits", None) or attention_splits(
