@@ -116,8 +116,82 @@ HFEE_API int hfee_rope_table(const int* positions, const double* inv_freq, float
 // (2i, 2i+1) otherwise; dims at or above rope_dim pass through.  k/v pools may be
 // null when this layer reads another layer's cache (q only).
 // Reference: internal/llm/forward.go:90-102,181-196.
-template <typename T>
+// VEC: elements per 16-byte access (8 for bfloat16, 4 for float32).  A work item is one 16-byte piece
+// of the first member of each pair together with the matching piece of the second member:
+// half-split pairing pairs piece [a, a+VEC) with [a+half, a+half+VEC); interleaved pairing keeps both
+// members in one piece.  Dims at or above rope_dim (and all of v) are copied piece by piece.
+template <typename T, int VEC>
+struct alignas(16) Piece { T v[VEC]; };
+
+template <typename T, int VEC>
 __global__ void rope_cache_kernel(const T* __restrict__ qkv, int ld_qkv, const float2* __restrict__ cs,
+                                  const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                                  T* __restrict__ q_out, int ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                  PagedCache cache, int heads, int rope_dim, int interleaved) {
+  using P = Piece<T, VEC>;
+  const int i = blockIdx.x;
+  const int hd = cache.head_dim, kvh = cache.kv_heads;
+  const int half = rope_dim / 2;
+  const int per_block = (int)blockDim.x * gridDim.y;    // work items are spread over the blocks of grid.y
+  const int pos = positions[i];                          // host-written: readable before the previous kernel ends
+  const int slot = slot_of_token[i];
+  const int page_warm = k_pool ? cache.block_table[(long long)slot * cache.max_pages + (pos >> cache.page_shift)] : 0;
+  asm volatile("" ::"r"(page_warm));
+  pdl_wait();
+  pdl_launch_dependents();
+  const T* row = qkv + (long long)i * ld_qkv;
+  const int total_heads = k_pool ? heads + 2 * kvh : heads;   // q only when this run reads another run's cache
+  const int pieces = hd / VEC;                                 // 16-byte pieces per head
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total_heads * pieces; w += per_block) {
+    const int h = w / pieces, a = (w % pieces) * VEC;          // first dim of this piece
+    const T* src = row + (long long)h * hd;
+    T* dst;
+    if (h < heads) {
+      dst = q_out + (long long)i * ld_q + (long long)h * hd;
+    } else {
+      const int kh = h < heads + kvh ? h - heads : h - heads - kvh;
+      dst = (h < heads + kvh ? k_pool : v_pool) + paged_offset(cache, slot, pos, kh);
+    }
+    const bool rotate = cs != nullptr && h < heads + kvh && a < rope_dim;
+    if (!rotate) {
+      *reinterpret_cast<P*>(dst + a) = *reinterpret_cast<const P*>(src + a);
+      continue;
+    }
+    const float2* t = cs + (long long)i * half;
+    if (interleaved) {                                         // pairs (2p, 2p+1) inside the piece
+      P x = *reinterpret_cast<const P*>(src + a), y;
+      float2 cc[VEC / 2];                                    // the piece's table entries, 16 bytes at a time
+#pragma unroll
+      for (int e = 0; e < VEC / 2; e += 2) *reinterpret_cast<float4*>(&cc[e]) = *reinterpret_cast<const float4*>(t + a / 2 + e);
+#pragma unroll
+      for (int e = 0; e < VEC; e += 2) {
+        const float2 c = cc[e / 2];
+        const float x0 = to_f32<T>(x.v[e]), x1 = to_f32<T>(x.v[e + 1]);
+        y.v[e] = from_f32<T>(x0 * c.x - x1 * c.y);
+        y.v[e + 1] = from_f32<T>(x0 * c.y + x1 * c.x);
+      }
+      *reinterpret_cast<P*>(dst + a) = y;
+    } else if (a < half) {                                     // pairs (a+e, a+e+half): this item does both pieces
+      P x0 = *reinterpret_cast<const P*>(src + a), x1 = *reinterpret_cast<const P*>(src + a + half), y0, y1;
+      float2 cc[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; e += 2) *reinterpret_cast<float4*>(&cc[e]) = *reinterpret_cast<const float4*>(t + a + e);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float2 c = cc[e];
+        const float u = to_f32<T>(x0.v[e]), v = to_f32<T>(x1.v[e]);
+        y0.v[e] = from_f32<T>(u * c.x - v * c.y);
+        y1.v[e] = from_f32<T>(u * c.y + v * c.x);
+      }
+      *reinterpret_cast<P*>(dst + a) = y0;
+      *reinterpret_cast<P*>(dst + a + half) = y1;
+    }                                                          // pieces in [half, rope_dim) were written by their partner
+  }
+}
+
+// Element-pair version for shapes whose rows or rotary halves are not whole 16-byte pieces.
+template <typename T>
+__global__ void rope_cache_scalar_kernel(const T* __restrict__ qkv, int ld_qkv, const float2* __restrict__ cs,
                                   const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                                   T* __restrict__ q_out, int ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   PagedCache cache, int heads, int rope_dim, int interleaved) {
@@ -179,18 +253,36 @@ HFEE_API int hfee_rope_cache_write(const void* qkv, int ld_qkv, const float* cs,
   HFEE_REQUIRE(rope_dim >= 0 && rope_dim <= head_dim && rope_dim % 2 == 0,
                "rope: rope_dim %d must be even and at most head_dim %d", rope_dim, head_dim);
   HFEE_REQUIRE(heads > 0 && kv_heads > 0 && page_size > 0 && max_pages > 0, "rope: bad sizes");
+  const int vec = dtype == HFEE_F32 ? 4 : 8;                   // elements per 16 bytes
+  // few tokens (decode): the element-pair kernel spreads the little work there is over more threads
+  const bool vector = n >= 64 && head_dim % vec == 0 && (rope_dim / 2) % vec == 0 && ld_qkv % vec == 0 && ld_q % vec == 0 &&
+                      (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pool % 16 == 0 &&
+                      (uintptr_t)v_pool % 16 == 0;
   PagedCache c;
   HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
                "page_size %d must be a power of two", page_size);
+  int items = (heads + 2 * kv_heads) * (vector ? head_dim / vec : head_dim / 2);
   int threads = 256;
-  int items = (heads + 2 * kv_heads) * (head_dim / 2);
   dim3 grid((unsigned)n, (unsigned)((items + threads - 1) / threads));
   if (grid.y > 64) grid.y = 64;
+  if (!vector) {
+    if (dtype == HFEE_F32)
+      hfee_launch(rope_cache_scalar_kernel<float>, dim3(grid), dim3(threads), 0, stream, (const float*)qkv, ld_qkv,
+                  (const float2*)cs, positions, slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c,
+                  heads, rope_dim, interleaved);
+    else if (dtype == HFEE_BF16)
+      hfee_launch(rope_cache_scalar_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream,
+                  (const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs, positions, slot_of_token, (__nv_bfloat16*)q_out,
+                  ld_q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, c, heads, rope_dim, interleaved);
+    else
+      return hfee_fail(HFEE_ERR_ARG, "rope: unknown dtype %d", dtype);
+    return hfee_check_launch("rope_cache_write");
+  }
   if (dtype == HFEE_F32)
-    hfee_launch(rope_cache_kernel<float>, dim3(grid), dim3(threads), 0, stream, (const float*)qkv, ld_qkv, (const float2*)cs, positions,
+    hfee_launch(rope_cache_kernel<float, 4>, dim3(grid), dim3(threads), 0, stream, (const float*)qkv, ld_qkv, (const float2*)cs, positions,
         slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c, heads, rope_dim, interleaved);
   else if (dtype == HFEE_BF16)
-    hfee_launch(rope_cache_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
+    hfee_launch(rope_cache_kernel<__nv_bfloat16, 8>, dim3(grid), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, ld_qkv, (const float2*)cs,
         positions, slot_of_token, (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, c,
         heads, rope_dim, interleaved);
   else

@@ -67,7 +67,9 @@ def test_rope_table_far_positions(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,hd,rope_dim,inter", [(4, 2, 16, 16, False), (3, 1, 32, 32, True),
-                                                         (2, 2, 48, 16, False), (5, 5, 64, 32, True)])
+                                                         (2, 2, 48, 16, False), (5, 5, 64, 32, True),
+                                                         (2, 1, 24, 8, False), (3, 1, 20, 12, True),   # not 16-byte pieces
+                                                         (32, 8, 64, 64, False), (8, 2, 128, 64, False)])
 def test_rope_cache_write(ops, dtype, heads, kv, hd, rope_dim, inter):
     g = torch.Generator().manual_seed(2)
     n, page, max_pages, slots = 23, 16, 4, 3
