@@ -302,3 +302,145 @@ def test_toy_architecture_with_state_runs_through_the_engine(tmp_path, dtype):
         runner.step([__import__("hfee_b200").StepEntry(s, seqs[3][t:t + 2], [])])
         assert int((windowed.table[s] >= 0).sum()) <= 3
     runner.close(s)
+
+
+# ---------------------------------------------------------------------------------------------
+# A second toy architecture: a feed-forward with routing and another position encoding, both
+# defined here, beside the framework's attention.
+
+def _register_routed_toy():
+    from hfee_b200 import (LayerSpec, ModelSpec, Part, PartSpec, TensorNeed, register_architecture, register_part)
+    from hfee_b200.parts import part_class
+    from hfee_b200.parts.rotary import Rotary
+
+    class RoutedFeedForward(Part):
+        """Top-1 routing over small gated experts: router logits in float32, each token runs
+        through the expert with the largest logit, scaled by that logit's softmax weight."""
+        category = "feed_forward"
+
+        @staticmethod
+        def tensor_needs(spec):
+            e, w, i = spec.experts, spec.width, spec.inner
+            return {"router": TensorNeed((e, w), role="vector"), "gate": TensorNeed((e * i, w)),
+                    "up": TensorNeed((e * i, w)), "down": TensorNeed((e * w, i))}
+
+        def __init__(self, spec, tensors, rt):
+            super().__init__(spec, tensors, rt)
+            e, w, i = spec.experts, spec.width, spec.inner
+            self.router = tensors["router"].float()
+            self.gate = tensors["gate"].float().reshape(e, i, w)
+            self.up = tensors["up"].float().reshape(e, i, w)
+            self.down = tensors["down"].float().reshape(e, w, i)
+
+        def forward(self, xn, residual, step):
+            x = xn.float()
+            logits = x @ self.router.t()                       # float32 router
+            weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+            for e in range(self.router.shape[0]):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows]
+                g, u = xe @ self.gate[e].t(), xe @ self.up[e].t()
+                residual[rows] += ((g / (1 + torch.exp(-g)) * u) @ self.down[e].t()) * weight[rows, None]
+
+    class ScaledRotary(Rotary):
+        """Rotary encoding with positions divided by ``factor`` (linear position interpolation)."""
+
+        def __init__(self, spec, tensors, rt):
+            super().__init__(spec, tensors, rt)
+            self.inv_freq_host = [f / spec.factor for f in self.inv_freq_host]
+            self.inv_freq = torch.tensor(self.inv_freq_host, dtype=torch.float64, device=rt.device)
+
+    for cat, kind, cls in (("feed_forward", "toy_routed", RoutedFeedForward), ("position", "scaled_rotary", ScaledRotary)):
+        try:
+            part_class(cat, kind)
+        except ValueError:
+            register_part(cat, kind, cls)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        d: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(dict(d))
+
+    def spec_of(c):
+        d = c.d
+        w = d["width"]
+        pos = PartSpec("scaled_rotary", head_dim=d["head_dim"], rope_dim=d["head_dim"], theta=777.0, scaling=None,
+                       pairing="interleaved", factor=d["factor"])
+        attn = PartSpec("attention", width=w, heads=d["heads"], kv_heads=d["kv_heads"], head_dim=d["head_dim"],
+                        position=pos, window=None, scale=None)
+        dense = PartSpec("swiglu", width=w, inner=d["inner"])
+        routed = PartSpec("toy_routed", width=w, inner=d["expert_inner"], experts=d["experts"])
+        norm = PartSpec("rms_norm", width=w, eps=d["eps"], add_unit=True)
+        layers = []
+        for i in range(d["layers"]):
+            p = f"l{i}."
+            ffn = routed if i % 2 == 1 else dense                # dense and routed layers alternate
+            names = {"mixer.q": p + "q", "mixer.k": p + "k", "mixer.v": p + "v", "mixer.o": p + "o",
+                     "mixer_norm.weight": p + "n1", "ffn_norm.weight": p + "n2"}
+            names.update({"ffn." + k: p + "ffn_" + k for k in (("router", "gate", "up", "down") if i % 2 else ("gate", "up", "down"))})
+            layers.append(LayerSpec(block=PartSpec("pre_norm", width=w), mixer=attn, feed_forward=ffn, mixer_norm=norm,
+                                    ffn_norm=norm, names=names))
+        return ModelSpec(width=w, vocab=d["vocab_size"], embedding=PartSpec("token", vocab=d["vocab_size"], width=w),
+                         layers=tuple(layers), schedule=ModelSpec.sequential(len(layers)), final_norm=norm,
+                         head=PartSpec("linear", vocab=d["vocab_size"], width=w, tied=False),
+                         names={"embedding.table": "emb", "final_norm.weight": "norm", "head.weight": "head"}, max_positions=512)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig.from_dict, spec_of)
+
+
+ROUTED = {"architectures": ["ToyRoutedForCausalLM"], "width": 48, "heads": 6, "kv_heads": 3, "head_dim": 16,
+          "inner": 100, "experts": 3, "expert_inner": 40, "layers": 4, "vocab_size": 97, "eps": 1e-6, "factor": 4.0}
+
+
+def routed_plain_forward(w, tokens):
+    c = ROUTED
+    n = len(tokens)
+    inv = plain.rope_inv_freq(c["head_dim"], 777.0) / c["factor"]
+    norm = lambda x, name: plain.rms_norm(x, 1.0 + w[name], c["eps"])         # add_unit: scale by 1 + w
+    x = plain.embed(w["emb"], tokens)
+    for i in range(c["layers"]):
+        p = f"l{i}."
+        xb = norm(x, p + "n1")
+        q = plain.rope(plain.linear(xb, w[p + "q"]), c["heads"], c["head_dim"], range(n), inv, "interleaved")
+        k = plain.rope(plain.linear(xb, w[p + "k"]), c["kv_heads"], c["head_dim"], range(n), inv, "interleaved")
+        att = plain.attention(q, k, plain.linear(xb, w[p + "v"]), c["heads"], c["kv_heads"], c["head_dim"])
+        x = x + plain.linear(att, w[p + "o"])
+        xb = norm(x, p + "n2")
+        if i % 2 == 0:
+            x = x + plain.feed_forward(xb, w[p + "ffn_gate"], w[p + "ffn_up"], w[p + "ffn_down"])
+        else:
+            e_n, ei = c["experts"], c["expert_inner"]
+            logits = xb @ w[p + "ffn_router"].T
+            probs = np.exp(logits - logits.max(1, keepdims=True))
+            probs /= probs.sum(1, keepdims=True)
+            out = np.zeros_like(x)
+            for t in range(n):
+                e = int(np.argmax(logits[t]))
+                g = w[p + "ffn_gate"].reshape(e_n, ei, -1)[e] @ xb[t]
+                u = w[p + "ffn_up"].reshape(e_n, ei, -1)[e] @ xb[t]
+                out[t] = (w[p + "ffn_down"].reshape(e_n, -1, ei)[e] @ plain.swiglu(g, u)) * probs[t, e]
+            x = x + out
+    return plain.linear(norm(x, "norm"), w["head"])
+
+
+def test_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """Float32 (the bfloat16 rounding of the router's input could flip a near-tied expert choice)."""
+    from hfee_b200 import EngineConfig, ModelRunner, write_random_model
+    _register_routed_toy()
+    d = str(tmp_path / "routed")
+    write_random_model(d, ROUTED, seed=6, dtype="float32", std=0.08)
+    w = plain.read_safetensors(d + "/model.safetensors")
+    rng = np.random.default_rng(4)
+    seqs = [rng.integers(0, 97, size=n).tolist() for n in (45, 12, 30)]
+    refs = [routed_plain_forward(w, s) for s in seqs]
+    runner = ModelRunner(d, EngineConfig(dtype="float32", page_size=16, max_requests=3, max_context=64,
+                                         max_cache_tokens=7 * 16, max_batch_tokens=64, use_cuda_graphs=False))
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(5, 2, 9, 2, 20)), ru.mixed(seqs, live=3, seed=2)):
+        got = ru.run_in_process(runner, steps)
+        for i in range(len(seqs)):
+            assert ru.rel_err(got[i], refs[i]) < 1e-4, f"request {i}"
