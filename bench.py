@@ -70,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -132,7 +132,7 @@ def reference_arm():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
@@ -241,7 +241,7 @@ def main():
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(decode_point(b, min(args.steps, 32), args.warmup)["tok_s"], 1)
+            points[f"decode_b{b}"] = round(decode_point(b, min(args.steps, 64), args.warmup)["tok_s"], 1)
 
     # ---------------------------------------------------------------- end to end through generate()
     # Host tokens in, host tokens out: every step copies its token ids and positions from pinned
