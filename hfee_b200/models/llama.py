@@ -33,9 +33,8 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
             "mixer_norm.weight": p + "input_layernorm.weight",
             "ffn_norm.weight": p + "post_attention_layernorm.weight",
         }))
-    names = {"embedding.table": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight"}
-    if not cfg.tie_word_embeddings:
-        names["head.weight"] = "lm_head.weight"
+    names = {"embedding.table": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight",
+             "head.weight": "lm_head.weight"}            # optional in the file when the embeddings are tied
     return ModelSpec(
         width=cfg.hidden_size, vocab=cfg.vocab_size,
         embedding=PartSpec("token", vocab=cfg.vocab_size, width=cfg.hidden_size),

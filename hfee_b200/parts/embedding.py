@@ -35,18 +35,20 @@ class LinearHead(Part):
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
-        if spec.get("tied", False):
-            return {}
-        return {"weight": TensorNeed((spec.vocab, spec.width))}
+        # tied: the checkpoint need not hold a head; if it does, that tensor is used, as the
+        # reference uses output.weight whenever the file has one (internal/llm/model.go:118-121)
+        return {"weight": TensorNeed((spec.vocab, spec.width), optional=bool(spec.get("tied", False)))}
 
     def __init__(self, spec, tensors, rt, embedding: TokenEmbedding = None):
         super().__init__(spec, tensors, rt)
-        if spec.get("tied", False):
+        if "weight" in tensors:
+            self.weight = tensors["weight"]
+        elif spec.get("tied", False):
             if embedding is None:
                 raise ValueError("a tied head needs the embedding part")
             self.weight = embedding.table
         else:
-            self.weight = tensors["weight"]
+            raise ValueError("the head has no weight and is not tied to the embedding")
 
     accepts_lazy_input = True        # the final norm may be fused into the product
 

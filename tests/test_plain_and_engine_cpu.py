@@ -129,3 +129,22 @@ def test_generate_on_cpu_doubles_pipelined_and_not(tiny_dirs, cpu_ops, pipeline)
         assert r.token_ids == wnt[:cut]
         assert r.stats.done_reason == ("stop" if cut < len(wnt) else "length") and r.stats.eval_tokens == cut
     shutil.rmtree(d)
+
+
+def test_tied_model_with_a_stored_head_uses_it(tiny_dirs, cpu_ops, tmp_path):
+    """tie_word_embeddings with lm_head.weight in the file: accepted, and the stored head is used
+    (the reference takes output.weight whenever the file has one, internal/llm/model.go:118-121)."""
+    import os, shutil, torch
+    from hfee_b200.weights import TensorFiles, write_file
+    d = str(tmp_path / "m")
+    shutil.copytree(tiny_dirs["B"], d)
+    files = TensorFiles(d)
+    tensors = {n: files.tensor(n).clone() for n in files.names()}
+    tensors["lm_head.weight"] = torch.randn(384, 96, generator=torch.Generator().manual_seed(0)) * 0.02
+    write_file(os.path.join(d, "model.safetensors"), tensors)
+    cfg, w = plain.load_model_dir(d)
+    toks = list(range(3, 20))
+    ref = plain.forward(cfg, w, toks)                       # the plain model prefers lm_head.weight too
+    r = _runner(d)
+    out = r.step([StepEntry(r.open(), toks, list(range(len(toks))))]).numpy()
+    assert _rel(out, ref) < 2e-5
