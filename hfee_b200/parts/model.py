@@ -30,6 +30,8 @@ def _named(needs: Mapping[str, TensorNeed], prefix: str, names: Mapping[str, str
     for key, need in needs.items():
         local = f"{prefix}.{key}"
         if local not in names:
+            if need.optional:       # an architecture that never stores an optional tensor gives it no name
+                continue
             raise ValueError(f"{where}: the architecture gives no checkpoint name for tensor {local!r}")
         out[local] = (names[local], need)
     return out

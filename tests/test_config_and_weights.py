@@ -102,6 +102,13 @@ def test_tensor_needs_cover_the_checkpoint_names():
     assert len(needs) == 3 + 2 * 9
     tied = model_tensor_needs(llama_spec(LlamaConfig.from_dict(TINY_B)))
     assert tied["lm_head.weight"].optional and len(tied) == 3 + 3 * 9      # a tied model may still store a head
+    # an architecture that gives an optional tensor no name simply never reads it; a required one must be named
+    import dataclasses
+    spec = llama_spec(LlamaConfig.from_dict(TINY_B))
+    unnamed = dataclasses.replace(spec, names={k: v for k, v in spec.names.items() if k != "head.weight"})
+    assert "lm_head.weight" not in model_tensor_needs(unnamed) and len(model_tensor_needs(unnamed)) == 2 + 3 * 9
+    with pytest.raises(ValueError, match="no checkpoint name"):
+        model_tensor_needs(dataclasses.replace(spec, names={k: v for k, v in spec.names.items() if k != "final_norm.weight"}))
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
