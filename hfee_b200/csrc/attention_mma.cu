@@ -103,8 +103,11 @@ attention_mma_kernel(AttnParams p) {
   const int g = lane >> 2, c = lane & 3;
   const int wrow = KSPLIT ? 0 : warp * 16;            // first tile row of this warp
   const int wkey = KSPLIT ? warp * 16 : 0;            // first key (within a block) of this warp
-  const int tile = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
-  const int kvh = blockIdx.y, r = blockIdx.z;
+  // CTAs start in the order of blockIdx.x, then y: the tiles with the most keys (the latest
+  // positions) of every kv head first, the light ones last to fill the gaps at the end
+  const int tile = (int)(gridDim.y / p.num_splits) - 1 - (int)(blockIdx.y / p.num_splits);
+  const int split = blockIdx.y % p.num_splits;
+  const int kvh = blockIdx.x, r = blockIdx.z;
 
   const int tok0 = p.cu_tokens[r], n_new = p.cu_tokens[r + 1] - tok0;
   const int t_first = tile * p.tokens_per_tile;
@@ -354,7 +357,7 @@ attention_mma_kernel(AttnParams p) {
       __threadfence();
       __syncthreads();
       if (tid == 0) {
-        int* counter = p.split_done + (long long)r * gridDim.y + kvh;
+        int* counter = p.split_done + (long long)r * gridDim.x + kvh;
         is_last = atomicAdd(counter, 1) == p.num_splits - 1;
         if (is_last) *counter = 0;
       }
@@ -425,7 +428,7 @@ int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStr
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((unsigned)(q_tiles * p.num_splits), (unsigned)kv_heads, (unsigned)requests);
+  dim3 grid((unsigned)kv_heads, (unsigned)(q_tiles * p.num_splits), (unsigned)requests);
   hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
   return hfee_check_launch("attention_mma");
 }
@@ -464,13 +467,14 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   int group = heads / kv_heads;
   HFEE_REQUIRE(group <= 64, "attention_mma: %d query heads per kv head exceed 64", group);
   HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 2 == 0 && ((uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
-  HFEE_REQUIRE(requests <= 65535 && kv_heads <= 65535, "attention_mma: too many requests or kv heads for one grid");
+  HFEE_REQUIRE(requests <= 65535, "attention_mma: too many requests for one grid");
   HFEE_REQUIRE(max_new > 0 && num_splits >= 1 && num_splits <= 32, "attention_mma: num_splits must be in 1..32");
   // when 16 rows hold every request's new tokens (decode) the warps split the keys instead
   bool ksplit = max_new * group <= 16;
   int rows = ksplit ? 16 : 64;
   int tokens_per_tile = rows / group;
   int q_tiles = (max_new + tokens_per_tile - 1) / tokens_per_tile;
+  HFEE_REQUIRE((long long)q_tiles * num_splits <= 65535, "attention_mma: %d new tokens of one request exceed one grid", max_new);
   HFEE_REQUIRE(num_splits == 1 || (ksplit && scratch != nullptr),
                "attention_mma: splitting the keys needs at most 16 query rows per (request, kv head) and scratch memory");
   HFEE_REQUIRE(num_splits == 1 || (long long)requests * kv_heads <= COUNTER_SLOTS,

@@ -94,8 +94,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   unsigned char* p_s = kv_s + KV_STAGES * 2 * KT_BYTES;                 // [2][P]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // heaviest tiles (latest positions) first
-  const int tile = p.q_tiles - 1 - (int)blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  // CTAs start in the order of blockIdx.x, then y: the heaviest tiles (latest positions) of every
+  // kv head first, the light ones last, so that they fill the gaps at the end
+  const int tile = p.q_tiles - 1 - (int)blockIdx.y, kvh = blockIdx.x, r = blockIdx.z;
   const int tok0 = p.cu_tokens[r], n_new = p.cu_tokens[r + 1] - tok0;
   const int t_first = tile * p.tokens_per_tile;
   if (t_first >= n_new) return;
@@ -386,7 +387,8 @@ HFEE_API int hfee_attention_tc(const void* q, int ld_q, const void* k_pool, cons
                "(got head_dim %d, heads %d/%d, page_size %d)", head_dim, heads, kv_heads, page_size);
   HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0,
                "attention_tc: q and out must be 16-byte aligned with leading dimensions %% 8 == 0");
-  HFEE_REQUIRE(requests <= 65535 && kv_heads <= 65535 && max_new > 0 && num_pages > 0, "attention_tc: bad sizes");
+  HFEE_REQUIRE(requests <= 65535 && max_new > 0 && max_new / (QM / (heads / kv_heads)) < 65535 && num_pages > 0,
+               "attention_tc: bad sizes");
   const int group = heads / kv_heads;
   TcAttnParams p;
   p.out = (__nv_bfloat16*)out; p.ld_o = ld_o;
@@ -425,7 +427,7 @@ HFEE_API int hfee_attention_tc(const void* q, int ld_q, const void* k_pool, cons
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_tc: cannot get %d bytes of shared memory: %s", AT_SMEM, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((unsigned)p.q_tiles, (unsigned)kv_heads, (unsigned)requests);
+  dim3 grid((unsigned)kv_heads, (unsigned)p.q_tiles, (unsigned)requests);
   hfee_launch(attention_tc_kernel, grid, dim3(AT_THREADS), AT_SMEM, stream, mq, mk, mv, p, status);
   return hfee_check_launch("attention_tc");
 }
