@@ -8,8 +8,8 @@
 // to absolute multiples of 64; a block's rows are fetched page by page with
 // cp.async (double buffered), rows outside the tile's key range are zero-filled so
 // that stale page content never reaches an MMA.  With num_splits > 1 the key blocks
-// of a tile are divided among CTAs which write unnormalised partial results; the CTA
-// that finishes a (request, kv head) group last merges them in split order.
+// of a tile are divided among CTAs which write unnormalised partial results; the
+// combine kernel merges them in split order.
 // Reference: hostfog/hfee internal/llm/forward.go:146-178, internal/ggml/ops.go:136-150.
 #include "common.cuh"
 
@@ -20,10 +20,6 @@
 namespace {
 
 constexpr int BLOCK_N = 64;
-// Scratch layout for split keys: COUNTER_SLOTS ints of per-(request, kv head) completion counters at
-// the very front - a fixed place whatever the call's sizes, so that parts written by one call can
-// never land where another call expects a zeroed counter - then the parts.
-constexpr int COUNTER_SLOTS = 4096;
 
 struct AttnParams {
   const __nv_bfloat16* q; int ld_q;
@@ -40,8 +36,6 @@ struct AttnParams {
   int num_splits;
   float* part_o;               // [(token*heads + head)*num_splits + split][HD]
   float* part_ml;              // [...][2] = (max in log2 units, sum)
-  int* split_done;             // [requests][kv_heads]: splits of a row group that have written their part;
-                               // zero between launches (the CTA that completes a group resets it)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -350,42 +344,6 @@ attention_mma_kernel(AttnParams p) {
         if (d == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
       }
     }
-    if (p.num_splits > 1) {
-      // The CTA that writes the last part of this (request, kv head) group merges all parts, in
-      // split order, and writes the output rows: no second kernel, and a fixed sum order.
-      __shared__ int is_last;
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        int* counter = p.split_done + (long long)r * gridDim.x + kvh;
-        is_last = atomicAdd(counter, 1) == p.num_splits - 1;
-        if (is_last) *counter = 0;
-      }
-      __syncthreads();
-      if (is_last) {
-        __threadfence();
-        for (int idx = tid; idx < rows_used * (HD / 2); idx += THREADS) {
-          int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
-          int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
-          long long base = ((long long)(tok0 + t) * p.heads + head) * p.num_splits;
-          float m = -INFINITY;
-          for (int sp = 0; sp < p.num_splits; ++sp) m = fmaxf(m, __ldcg(p.part_ml + (base + sp) * 2));
-          float l = 0.f, o0 = 0.f, o1 = 0.f;
-          for (int sp = 0; sp < p.num_splits; ++sp) {
-            float ms = __ldcg(p.part_ml + (base + sp) * 2);
-            if (ms == -INFINITY) continue;
-            float wgt = exp2f(ms - m);
-            float2 po = __ldcg(reinterpret_cast<const float2*>(p.part_o + (base + sp) * HD + d));
-            l += wgt * __ldcg(p.part_ml + (base + sp) * 2 + 1);
-            o0 += wgt * po.x;
-            o1 += wgt * po.y;
-          }
-          float inv = l > 0.f ? 1.f / l : 0.f;
-          __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
-          *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
-        }
-      }
-    }
   } else {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -412,6 +370,38 @@ attention_mma_kernel(AttnParams p) {
       }
     }
   }
+  }
+}
+
+// out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in order.
+// One warp per (token, head): lane s holds split s's (max, sum); the weights are then handed
+// round by shuffle while every lane accumulates its own output dims.
+constexpr int COMBINE_WARPS = 4;
+__global__ void __launch_bounds__(COMBINE_WARPS * 32)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd, int num_splits, int pairs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pair = blockIdx.x * COMBINE_WARPS + warp;
+  if (pair >= pairs) return;
+  int token = pair / heads, head = pair % heads;
+  long long base = (long long)pair * num_splits;
+  float ms = lane < num_splits ? part_ml[(base + lane) * 2] : -INFINITY;
+  float ls = lane < num_splits ? part_ml[(base + lane) * 2 + 1] : 0.f;
+  float m = warp_max(ms);
+  float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
+  float l = 0.f;
+  for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ls, s);     // split order
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d0 = 0; d0 < hd; d0 += 32) {          // every lane takes every trip: the shuffles need the whole warp
+    int d = d0 + lane;
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      float ws = __shfl_sync(0xffffffffu, w, s);
+      if (d < hd) acc += ws * part_o[(base + s) * hd + d];
+    }
+    if (d < hd) out[(long long)token * ld_o + (long long)head * hd + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -446,11 +436,9 @@ int dispatch_mode(const AttnParams& p, bool ksplit, int q_tiles, int kv_heads, i
 
 }  // namespace
 
-// Scratch floats needed for `num_splits` > 1: 4096 completion counters at the front (they must be
-// zero when the kernel starts; the kernel leaves them zero), then n_tokens * heads * num_splits *
-// (head_dim + 2) floats of parts.
+// Scratch floats needed for `num_splits` > 1: n_tokens * heads * num_splits * (head_dim + 2).
 HFEE_API long long hfee_attention_mma_scratch_floats(int n_tokens, int heads, int head_dim, int num_splits) {
-  return num_splits > 1 ? COUNTER_SLOTS + (long long)n_tokens * heads * num_splits * (head_dim + 2) : 0;
+  return num_splits > 1 ? (long long)n_tokens * heads * num_splits * (head_dim + 2) : 0;
 }
 
 // max_new: most new tokens of any request in the batch.  num_splits > 1 needs max_new * group <= rows
@@ -475,11 +463,8 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   int tokens_per_tile = rows / group;
   int q_tiles = (max_new + tokens_per_tile - 1) / tokens_per_tile;
   HFEE_REQUIRE((long long)q_tiles * num_splits <= 65535, "attention_mma: %d new tokens of one request exceed one grid", max_new);
-  HFEE_REQUIRE(num_splits == 1 || (ksplit && scratch != nullptr),
-               "attention_mma: splitting the keys needs at most 16 query rows per (request, kv head) and scratch memory");
-  HFEE_REQUIRE(num_splits == 1 || (long long)requests * kv_heads <= COUNTER_SLOTS,
-               "attention_mma: %d requests x %d kv heads exceed the %d completion counters of split mode", requests,
-               kv_heads, COUNTER_SLOTS);
+  HFEE_REQUIRE(num_splits == 1 || (q_tiles == 1 && scratch != nullptr),
+               "attention_mma: splitting the keys needs one query tile per request and scratch memory");
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.ld_q = ld_q;
   p.out = (__nv_bfloat16*)out; p.ld_o = ld_o;
@@ -490,9 +475,8 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   p.heads = heads; p.group = group;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.tokens_per_tile = tokens_per_tile; p.num_splits = num_splits;
-  p.split_done = reinterpret_cast<int*>(scratch);
-  p.part_o = scratch ? scratch + COUNTER_SLOTS : nullptr;
-  p.part_ml = scratch ? p.part_o + (long long)n_tokens * heads * num_splits * head_dim : nullptr;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (long long)n_tokens * heads * num_splits * head_dim : nullptr;
   int rc;
   switch (head_dim) {
 #define HFEE_CASE(D) case D: rc = dispatch_mode<D>(p, ksplit, q_tiles, kv_heads, requests, stream); break;
@@ -501,7 +485,11 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
 #undef HFEE_CASE
     default: return hfee_fail(HFEE_ERR_ARG, "attention_mma: head_dim %d", head_dim);
   }
-  return rc;
+  if (rc != HFEE_OK || num_splits == 1) return rc;
+  int pairs = n_tokens * heads;
+  hfee_launch(attention_combine_kernel, dim3((unsigned)((pairs + COMBINE_WARPS - 1) / COMBINE_WARPS)),
+              dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits, pairs);
+  return hfee_check_launch("attention_combine");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -547,11 +535,11 @@ HFEE_API int hfee_attention_decode_noalloc(const void* q, int ld_q, const void* 
   if (n_tokens == 0 || requests == 0) return HFEE_OK;
   HFEE_REQUIRE(num_splits >= 2, "attention_decode_noalloc: num_splits=%d; this entry point is the split-key variant (>= 2)", num_splits);
   HFEE_REQUIRE(n_tokens > 0 && heads > 0 && head_dim > 0, "attention_decode_noalloc: bad sizes");
-  long long need = COUNTER_SLOTS + (long long)n_tokens * heads * num_splits * (head_dim + 2);
+  long long need = (long long)n_tokens * heads * num_splits * (head_dim + 2);
   HFEE_REQUIRE(need <= (long long)HFEE_NOALLOC_SCRATCH_FLOATS,
-               "attention_decode_noalloc: 4096 counters + %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of "
-               "partial results exceed the built-in scratch of %d floats; use fewer splits or hfee_attention_mma "
-               "with scratch of your own", n_tokens, heads, num_splits, head_dim, need, (int)HFEE_NOALLOC_SCRATCH_FLOATS);
+               "attention_decode_noalloc: %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of partial "
+               "results exceed the built-in scratch of %d floats; use fewer splits or hfee_attention_mma with "
+               "scratch of your own", n_tokens, heads, num_splits, head_dim, need, (int)HFEE_NOALLOC_SCRATCH_FLOATS);
   float* scratch = nullptr;
   int rc = noalloc_scratch(&scratch);
   if (rc != HFEE_OK) return rc;

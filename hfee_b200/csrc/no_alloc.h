@@ -19,20 +19,16 @@
  * loads the library holds until the process ends.
  *
  * Limits and rules
- *  - 4096 + n_tokens * heads * num_splits * (head_dim + 2) must not exceed
- *    HFEE_NOALLOC_SCRATCH_FLOATS, and requests * kv_heads must not exceed 4096; larger requests are refused with HFEE_ERR_ARG and a message
+ *  - n_tokens * heads * num_splits * (head_dim + 2) must not exceed
+ *    HFEE_NOALLOC_SCRATCH_FLOATS; larger requests are refused with HFEE_ERR_ARG and a message
  *    (hfee_last_error()).  Nothing is launched in that case.
  *  - The function calls no cudaMalloc, cudaFree or other allocating routine.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  *    that device current) and remembers it per device.  Make that first call before any stream
  *    capture begins.
- *  - All calls share the one array, and it keeps what the last call left in it.  The partial
- *    results need no clearing: every (token, head, split) cell a call reads is first written by
- *    that call, empty key ranges included.  In front of them, at a fixed place that no call's
- *    partial results can reach, sit 4096 per-group completion counters that must be zero when a
- *    call starts: the array is zero when the library is loaded, and the CTA that completes a
- *    group sets its counter back to zero, so a call that ran to its end leaves them ready for
- *    the next whatever its sizes.  Two calls whose kernels overlap on the GPU (other
+ *  - All calls share the one array, and it keeps what the last call left in it.  Nothing in it
+ *    has to start at zero: every (token, head, split) cell a call later reads is first written
+ *    by that call, empty key ranges included.  Two calls whose kernels overlap on the GPU (other
  *    streams, other threads) race on the array; run them one after the other on one stream.
  */
 #pragma once

@@ -111,7 +111,7 @@ def _attention(args, decode: bool) -> dict:
     b.attention_splits = args.splits or None
     pos = i32([p for s, c in zip(before, new) for p in range(s, s + c)])
     sot = i32([i for i, c in enumerate(new) for _ in range(c)])
-    scratch = torch.zeros(ops.ATTN_COUNTER_SLOTS + r * heads * ops.MAX_SPLITS * (hd + 2), dtype=torch.float32, device=DEV) if decode else None
+    scratch = torch.empty(r * heads * ops.MAX_SPLITS * (hd + 2), dtype=torch.float32, device=DEV) if decode else None
     scale = 1.0 / math.sqrt(hd)
     fn = lambda i: ops.paged_attention(q, kp, vp, table, page, pos, sot, out, heads, kv, hd, scale, 0, step=b, scratch=scratch)
     sec = _time(fn, args.warmup, args.iters)

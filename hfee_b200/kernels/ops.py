@@ -417,7 +417,6 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
 
 
 MAX_SPLITS = 32
-ATTN_COUNTER_SLOTS = 4096     # per-(request, kv head) completion counters at the front of the split scratch
 
 
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
@@ -438,15 +437,15 @@ def attention_mma(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, c
     assert k_pool.is_contiguous() and v_pool.is_contiguous()
     assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
     if num_splits > 1:
-        # completion counters at the front (zero before the first use, left zero by every launch), then the parts
-        need = ATTN_COUNTER_SLOTS + n_tokens * heads * num_splits * (head_dim + 2)
-        assert requests * kv_heads <= ATTN_COUNTER_SLOTS
+        need = n_tokens * heads * num_splits * (head_dim + 2)
         assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
     _check(lib.hfee_attention_mma(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), block_table.shape[1], page_size, cu_tokens.data_ptr(),
                                   slots.data_ptr(), context_before.data_ptr(), out.data_ptr(),
                                   _rows(out, "attention out"), n_tokens, requests, max_new, heads, kv_heads,
                                   head_dim, float(scale), int(window or 0), num_splits, _ptr(scratch), _stream()), lib)
+    if num_splits > 1:
+        count_launches(1)
 
 
 USE_TC_ATTENTION = True
@@ -491,8 +490,7 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
         if step.max_new * group <= 16 and scratch is not None:
             splits = getattr(step, "attention_splits", None) or attention_splits(
                 step.r, kv_heads, getattr(step, "planning_context", step.max_context))
-            if (ATTN_COUNTER_SLOTS + step.n * heads * splits * (head_dim + 2) > scratch.numel()
-                    or step.r * kv_heads > ATTN_COUNTER_SLOTS):
+            if step.n * heads * splits * (head_dim + 2) > scratch.numel():
                 splits = 1
         attention_mma(q, k_pool, v_pool, block_table, page_size, step.cu_tokens, step.slots, step.context_before,
                       out, step.n, step.r, step.max_new, heads, kv_heads, head_dim, scale, window, splits, scratch)

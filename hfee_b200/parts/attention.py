@@ -47,9 +47,8 @@ class PagedAttention(Mixer):
         self.q_cols = self.heads * self.head_dim
         self.qkv_cols = (self.heads + 2 * self.kv_heads) * self.head_dim
         # partial results of a decode step whose keys are split among CTAs
-        self.split_scratch = rt.scratch("attn_partials", (ops.ATTN_COUNTER_SLOTS + rt.max_requests * self.heads *
-                                                          ops.MAX_SPLITS * (self.head_dim + 2),), torch.float32)
-        self.split_scratch[:ops.ATTN_COUNTER_SLOTS].zero_()     # completion counters: start (and stay) at zero
+        self.split_scratch = rt.scratch("attn_partials", (rt.max_requests * self.heads * ops.MAX_SPLITS *
+                                                          (self.head_dim + 2),), torch.float32)
 
     def cache_need(self) -> PagedKV:
         return PagedKV(self.kv_heads, self.head_dim, self.window)
