@@ -9,6 +9,9 @@
 // unchanged.  Partial sums of the warps are added in warp order, so every output is
 // summed in one fixed order whatever M is.
 //
+// Three kernels share the operand trick: this K-split one, a warp-per-tile one for many weight
+// rows, and, for at most 8 tokens, one that keeps the tokens in registers (see further down).
+//
 // Epilogues: store (bf16 or f32), accumulate into a float32 output (the residual
 // add), or SwiGLU over rows interleaved as [4 gate rows | 4 up rows] per group of 8.
 // Reference: out[t*Rows+r] = Dot(W[r,:], x[t,:]), hostfog/hfee internal/ggml/ops.go:54-70
@@ -391,6 +394,205 @@ gemm_stream_rows_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
   }
 }
 
+// The product for at most 8 tokens with the tokens held in registers.  In the two kernels above
+// every 16-byte weight load is matched by a 16-byte load of token values from L1, which costs a
+// quarter of the time of a large product.  Here warp w of a CTA owns the same 256 columns of
+// every 2048-column pass over K, so its token fragments (8 tokens x 256 values, 32 registers per
+// lane) are loaded once per pass and serve every weight row the CTA reads.  A CTA owns a
+// contiguous range of 8-row tiles (the ranges differ by at most one tile, whatever N is); the
+// warps' partial sums of a group of up to 8 tiles meet in shared memory (pass after pass in pass
+// order, then added in warp order: one fixed order whatever M is) and are written 64 columns wide.
+// NORM makes the token fragments on the fly from float32 rows, as in the first kernel above, but
+// once per CTA and pass instead of once per tile.
+constexpr int SL_WARPS = 8;
+constexpr int SL_STEPS = 8;                              // k32 steps per warp and pass
+constexpr int SL_SLICE = SL_STEPS * 32;                  // 256 columns per warp and pass
+constexpr int SL_PASS = SL_WARPS * SL_SLICE;             // 2048 columns per pass
+constexpr int SL_GROUP = 8;                              // row tiles whose sums are added together
+constexpr int SL_TOKEN_PITCH = SL_GROUP * 8 + 8;         // floats per token row of the partial sums (padded)
+
+template <int EPI, bool NORM, typename TOut>
+__global__ void __launch_bounds__(SL_WARPS * 32, 2)
+gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
+                          long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K, NormArgs norm) {
+  __shared__ __align__(16) float red[2][SL_WARPS][8][SL_TOKEN_PITCH];
+  __shared__ float inv_rms[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int n_tiles = (N + 7) / 8;
+  const int t_begin = (int)((long long)blockIdx.x * n_tiles / gridDim.x);
+  const int my_tiles = (int)((long long)(blockIdx.x + 1) * n_tiles / gridDim.x) - t_begin;
+  const int passes = (K + SL_PASS - 1) / SL_PASS;
+  const int total = my_tiles * passes;                   // (tile, pass) units of this warp
+
+  struct Unit { int grp, pass, tig; };                   // group of tiles, pass over K, tile in the group
+  auto group_size = [&](int grp) { return min(SL_GROUP, my_tiles - grp * SL_GROUP); };
+  auto advance = [&](Unit& s) {
+    if (++s.tig == group_size(s.grp)) {
+      s.tig = 0;
+      if (++s.pass == passes) { s.pass = 0; ++s.grp; }
+    }
+  };
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 wv[2][SL_STEPS];
+  auto load_unit = [&](bool valid, const Unit& s, uint4 (&dst)[SL_STEPS]) {
+    const int r = (t_begin + s.grp * SL_GROUP + s.tig) * 8 + g;
+    const bool rok = valid && r < N;
+    const __nv_bfloat16* wrow = W + (long long)(rok ? r : 0) * ldw + s.pass * SL_PASS + warp * SL_SLICE + c * 8;
+    const int k0 = s.pass * SL_PASS + warp * SL_SLICE + c * 8;
+#pragma unroll
+    for (int u = 0; u < SL_STEPS; ++u) dst[u] = (rok && k0 + u * 32 < K) ? ld_stream(wrow + u * 32) : zero;
+  };
+
+  Unit cur{0, 0, 0};
+  load_unit(total > 0, cur, wv[0]);
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // this lane's token (row g of the MMA's A tile; rows 8-15 stay zero)
+  const bool tok_ok = g < M;
+  const __nv_bfloat16* arow = A + (long long)(tok_ok ? g : 0) * lda;
+  const float* xrow = nullptr;
+  float scale = 0.f;
+  if constexpr (NORM) {
+    // 1/rms of token w by warp w: fixed order, so a row's scale does not depend on the batch
+    if (warp < M) {
+      const float* xr = norm.x + (long long)(norm.rows ? norm.rows[warp] : warp) * norm.ldx;
+      float ss = 0.f;
+      for (int k = lane * 4; k < K; k += 128) {
+        float4 v = __ldg((const float4*)(xr + k));
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(ss / (float)K + norm.eps);
+    }
+    __syncthreads();
+    if (tok_ok) {
+      xrow = norm.x + (long long)(norm.rows ? norm.rows[g] : g) * norm.ldx;
+      scale = inv_rms[g];
+    }
+  }
+  uint4 a_lo[SL_STEPS];
+  int a_pass = -1;
+  auto load_tokens = [&](int pass) {
+    const int k0 = pass * SL_PASS + warp * SL_SLICE + c * 8;
+#pragma unroll
+    for (int u = 0; u < SL_STEPS; ++u) {
+      const int k = k0 + u * 32;
+      if (!tok_ok || k >= K) { a_lo[u] = zero; continue; }
+      if constexpr (NORM) {
+        float4 x0 = __ldg((const float4*)(xrow + k)), x1 = __ldg((const float4*)(xrow + k + 4));
+        float4 n0 = __ldg((const float4*)(norm.weight + k)), n1 = __ldg((const float4*)(norm.weight + k + 4));
+        if (norm.add_unit) {
+          n0.x += 1.f; n0.y += 1.f; n0.z += 1.f; n0.w += 1.f;
+          n1.x += 1.f; n1.y += 1.f; n1.z += 1.f; n1.w += 1.f;
+        }
+        a_lo[u].x = pack2(x0.x * scale * n0.x, x0.y * scale * n0.y);
+        a_lo[u].y = pack2(x0.z * scale * n0.z, x0.w * scale * n0.w);
+        a_lo[u].z = pack2(x1.x * scale * n1.x, x1.y * scale * n1.y);
+        a_lo[u].w = pack2(x1.z * scale * n1.z, x1.w * scale * n1.w);
+      } else {
+        a_lo[u] = __ldg((const uint4*)(arow + k));
+      }
+    }
+    a_pass = pass;
+  };
+
+  // sums of a finished group: warps in warp order, then the epilogue, 64 (SwiGLU: 32) columns per token
+  auto finish_group = [&](int grp) {
+    const int gs = group_size(grp);
+    const int t0 = t_begin + grp * SL_GROUP;
+    const float (*part)[8][SL_TOKEN_PITCH] = red[grp & 1];
+    if constexpr (EPI == EPI_SWIGLU) {
+      // rows of a tile: [gate x4 | up x4] -> 4 outputs at columns tile*4 ..
+      const int t = threadIdx.x >> 5, o = threadIdx.x & 31;
+      const int tile = o >> 2, i = o & 3;
+      const long long col = (long long)(t0 + tile) * 4 + i;
+      if (t < M && tile < gs && col < N / 2) {
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < SL_WARPS; ++w) { gate += part[w][t][tile * 8 + i]; up += part[w][t][tile * 8 + 4 + i]; }
+        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = (threadIdx.x >> 6) + h * 4, o = threadIdx.x & 63;
+        const long long col = (long long)t0 * 8 + o;
+        if (t < M && o < gs * 8 && col < N) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < SL_WARPS; ++w) v += part[w][t][o];
+          const long long at = (long long)t * ldc + col;
+          if constexpr (EPI == EPI_ACCUM) C[at] = to_f32<TOut>(C[at]) + v;
+          else C[at] = from_f32<TOut>(v);
+        }
+      }
+    }
+  };
+
+  auto process = [&](const Unit& s, const uint4 (&src)[SL_STEPS]) {
+    if (s.pass != a_pass) load_tokens(s.pass);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < SL_STEPS; ++u) {
+      mma_bf16(acc, a_lo[u].x, 0u, a_lo[u].y, 0u, src[u].x, src[u].y);
+      mma_bf16(acc, a_lo[u].z, 0u, a_lo[u].w, 0u, src[u].z, src[u].w);
+    }
+    // acc[0], acc[1] = (token g, rows 2c, 2c+1) of the tile over this warp's columns of this pass
+    float2* dst = reinterpret_cast<float2*>(&red[s.grp & 1][warp][g][s.tig * 8 + 2 * c]);
+    if (s.pass == 0) *dst = make_float2(acc[0], acc[1]);
+    else { float2 old = *dst; *dst = make_float2(old.x + acc[0], old.y + acc[1]); }
+    if (s.pass == passes - 1 && s.tig == group_size(s.grp) - 1) {
+      // the other buffer is free again once every warp has passed this barrier: its sums were
+      // read before the barrier of the group before
+      __syncthreads();
+      finish_group(s.grp);
+    }
+  };
+
+  for (int j = 0; j < total; j += 2) {
+    Unit n1 = cur;
+    advance(n1);
+    load_unit(j + 1 < total, n1, wv[1]);
+    process(cur, wv[0]);
+    if (j + 1 < total) {
+      Unit n2 = n1;
+      advance(n2);
+      load_unit(j + 2 < total, n2, wv[0]);
+      process(n1, wv[1]);
+      cur = n2;
+    }
+  }
+}
+
+template <bool NORM>
+int launch_slices(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
+                  int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  static int resident = 0;
+  if (resident == 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    resident = 2 * (sms > 0 ? sms : 148);
+  }
+  const int n_tiles = (N + 7) / 8;
+  unsigned grid = (unsigned)(n_tiles < resident ? n_tiles : resident);
+#define HFEE_GO(EPI, T) hfee_launch(gemm_stream_slices_kernel<EPI, NORM, T>, dim3(grid), dim3(SL_WARPS * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K, norm)
+  if (epilogue == EPI_ACCUM) {
+    if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
+    HFEE_GO(EPI_ACCUM, float);
+  } else if (epilogue == EPI_SWIGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
+  }
+#undef HFEE_GO
+  return hfee_check_launch("gemm_stream_slices");
+}
+
 template <int MT, int NT, int NW, bool NORM>
 int launch(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
            int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
@@ -474,11 +676,12 @@ HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long 
   if (rc != HFEE_OK) return rc;
   HFEE_REQUIRE(lda % 8 == 0 && lda >= K && (uintptr_t)A % 16 == 0,
                "gemm_stream: the tokens' leading dimension %lld must be a multiple of 8, at least K, and 16-byte aligned", lda);
+  NormArgs none{nullptr, 0, nullptr, nullptr, 0.f, 0};
+  if (M <= 8) return launch_slices<false>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, none, stream);
   if ((N + 7) / 8 >= ROWS_MIN_TILES && M <= 32) {
     if (M <= 16) return launch_rows<1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
     return launch_rows<2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
   }
-  NormArgs none{nullptr, 0, nullptr, nullptr, 0.f, 0};
   return by_tokens<false>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, none, stream);
 }
 
@@ -492,5 +695,6 @@ HFEE_API int hfee_gemm_stream_norm(const float* X, long long ldx, const int* row
   HFEE_REQUIRE(ldx % 4 == 0 && ldx >= K && (uintptr_t)X % 16 == 0 && (uintptr_t)norm_weight % 16 == 0,
                "gemm_stream_norm: float32 rows need a leading dimension %% 4 == 0 and 16-byte alignment");
   NormArgs norm{X, ldx, rows, norm_weight, eps, add_unit};
+  if (M <= 8) return launch_slices<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
   return by_tokens<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
 }

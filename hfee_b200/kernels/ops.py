@@ -292,15 +292,15 @@ def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
                                      _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
 
 
-# Norming inside the streaming GEMM saves a launch but makes every CTA re-read and re-norm the
-# float32 rows from L2 within its load loop; measured on B200 at batch 8 the decode step went from
-# 1.06 ms to 1.46 ms, so the fusion is off and the norm kernel runs on its own.
-FUSE_NORM_INTO_STREAM_GEMM = False
+# Norming inside the streaming GEMM saves a launch, but every CTA then reads and norms the float32
+# rows itself after its wait on the previous kernel; measured on B200 at batch 8 the decode step got
+# slower (0.96 -> 1.15 ms), so the fusion is off (0 tokens) and the norm kernel runs on its own.
+FUSE_NORM_MAX_TOKENS = 0
 
 
 def _norm_fusable(inp, w: torch.Tensor) -> bool:
     """True when ``inp`` (a lazily normed input, see parts/norm.py) can be normed inside the streaming GEMM."""
-    if not FUSE_NORM_INTO_STREAM_GEMM:
+    if inp.n > FUSE_NORM_MAX_TOKENS:
         return False
     p = inp.fused_params()
     x = inp.source
