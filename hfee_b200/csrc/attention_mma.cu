@@ -134,19 +134,6 @@ attention_mma_kernel(AttnParams p) {
     int warm = p.cache.block_table[(long long)slot * p.cache.max_pages + (b_lo + tid) * BLOCK_N / p.cache.page_size];
     asm volatile("" ::"r"(warm));
   }
-  pdl_wait();
-  pdl_launch_dependents();
-
-  // ---- stage Q (rows beyond rows_used are zero)
-  for (int idx = tid; idx < ROWS * CHUNKS; idx += THREADS) {
-    int row = idx / CHUNKS, ch = idx % CHUNKS;
-    bool ok = row < rows_used;
-    int t = t_first + row / p.group, hg = row % p.group;
-    const __nv_bfloat16* src = p.q + (long long)(tok0 + (ok ? t : t_first)) * p.ld_q +
-                               (long long)(kvh * p.group + (ok ? hg : 0)) * HD + ch * 8;
-    cp_async16(q_s + row * PITCH + ch * 8, src, ok);
-  }
-
   // A block's 64 rows x CHUNKS 16-byte pieces are spread over the threads.  Page ids are looked
   // up first for all of a thread's pieces (independent loads), then the copies are issued.
   constexpr int PIECES = (BLOCK_N * CHUNKS + THREADS - 1) / THREADS;
@@ -190,11 +177,38 @@ attention_mma_kernel(AttnParams p) {
   }
 
   // one cp.async group per block, committed even when empty, so that "all but the newest
-  // STAGES-1 groups are complete" always means "this iteration's block has landed"
+  // STAGES-1 groups are complete" always means "this iteration's block has landed".
+  // Keys below context_before were written by earlier steps, not by the previous kernel: blocks
+  // that hold only such keys are requested before the wait on that kernel.
+  int requested = 0;
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (b_lo + i <= b_hi) load_kv(b_lo + i, i);
-    cp_async_commit();
+    if (requested == i && b_lo + i <= b_hi && (b_lo + i + 1) * BLOCK_N <= before) {
+      load_kv(b_lo + i, i);
+      cp_async_commit();
+      ++requested;
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // ---- stage Q (rows beyond rows_used are zero) with plain loads: it becomes visible with the
+  // first block's barrier and belongs to no cp.async group
+  for (int idx = tid; idx < ROWS * CHUNKS; idx += THREADS) {
+    int row = idx / CHUNKS, ch = idx % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows_used) {
+      int t = t_first + row / p.group, hg = row % p.group;
+      v = *reinterpret_cast<const uint4*>(p.q + (long long)(tok0 + t) * p.ld_q + (long long)(kvh * p.group + hg) * HD + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(q_s + row * PITCH + ch * 8) = v;
+  }
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i >= requested) {
+      if (b_lo + i <= b_hi) load_kv(b_lo + i, i);
+      cp_async_commit();
+    }
   }
 
   for (int b = b_lo; b <= b_hi; ++b) {
@@ -374,8 +388,9 @@ attention_mma_kernel(AttnParams p) {
 }
 
 // out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in order.
-// One warp per (token, head): lane s holds split s's (max, sum); the weights are then handed
-// round by shuffle while every lane accumulates its own output dims.
+// One warp per (token, head): lane s holds split s's (max, sum); every lane owns four output dims
+// per trip.  The partial outputs of up to 8 splits are requested together with the (max, sum)
+// pairs, before anything is computed: one memory round trip instead of one per split.
 constexpr int COMBINE_WARPS = 4;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -387,21 +402,39 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
   if (pair >= pairs) return;
   int token = pair / heads, head = pair % heads;
   long long base = (long long)pair * num_splits;
-  float ms = lane < num_splits ? part_ml[(base + lane) * 2] : -INFINITY;
-  float ls = lane < num_splits ? part_ml[(base + lane) * 2 + 1] : 0.f;
-  float m = warp_max(ms);
-  float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
-  float l = 0.f;
-  for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ls, s);     // split order
-  float inv = l > 0.f ? 1.f / l : 0.f;
-  for (int d0 = 0; d0 < hd; d0 += 32) {          // every lane takes every trip: the shuffles need the whole warp
-    int d = d0 + lane;
-    float acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      float ws = __shfl_sync(0xffffffffu, w, s);
-      if (d < hd) acc += ws * part_o[(base + s) * hd + d];
+  float2 ml = lane < num_splits ? *reinterpret_cast<const float2*>(part_ml + (base + lane) * 2) : make_float2(-INFINITY, 0.f);
+  float w = 0.f, inv = 0.f;
+  bool have_w = false;
+  for (int d0 = 0; d0 < hd; d0 += 128) {         // every lane takes every trip: the shuffles need the whole warp
+    const int d = d0 + lane * 4;                 // hd is a multiple of 16, so a lane's four dims are all in or all out
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = (s0 + i < num_splits && d < hd) ? *reinterpret_cast<const float4*>(part_o + (base + s0 + i) * hd + d)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!have_w) {
+        float m = warp_max(ml.x);
+        w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m);
+        float l = 0.f;
+        for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ml.y, s);     // split order
+        inv = l > 0.f ? 1.f / l : 0.f;
+        have_w = true;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float ws = __shfl_sync(0xffffffffu, w, (s0 + i) & 31);
+        if (s0 + i < num_splits) {
+          acc.x += ws * v[i].x; acc.y += ws * v[i].y; acc.z += ws * v[i].z; acc.w += ws * v[i].w;
+        }
+      }
     }
-    if (d < hd) out[(long long)token * ld_o + (long long)head * hd + d] = __float2bfloat16_rn(acc * inv);
+    if (d < hd) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+      uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      *reinterpret_cast<uint2*>(out + (long long)token * ld_o + (long long)head * hd + d) = pk;
+    }
   }
 }
 
