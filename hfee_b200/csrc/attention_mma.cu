@@ -496,6 +496,8 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   int tokens_per_tile = rows / group;
   int q_tiles = (max_new + tokens_per_tile - 1) / tokens_per_tile;
   HFEE_REQUIRE((long long)q_tiles * num_splits <= 65535, "attention_mma: %d new tokens of one request exceed one grid", max_new);
+  HFEE_REQUIRE(num_splits == 1 || (ld_o % 4 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)scratch % 16 == 0),
+               "attention_mma: with split keys the output needs 8-byte alignment (ld %% 4 == 0) and the scratch 16-byte alignment");
   HFEE_REQUIRE(num_splits == 1 || (q_tiles == 1 && scratch != nullptr),
                "attention_mma: splitting the keys needs one query tile per request and scratch memory");
   AttnParams p;
