@@ -24,17 +24,59 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     out[(long long)i * width + c] = ok ? to_f32<T>(row[c]) : 0.f;
 }
 
+// The same with 16-byte reads: one piece of the row per thread and trip, all of a thread's pieces
+// requested before the first is converted.
+template <typename T, int VEC>
+__global__ void embed_vec_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                 const int* __restrict__ slot_of_token, const int* __restrict__ feedback,
+                                 float* __restrict__ out, int width, int vocab) {
+  struct alignas(16) Piece { T v[VEC]; };
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x;
+  int tok = tokens[i];
+  if (tok < 0 && feedback != nullptr) tok = feedback[slot_of_token[i]];
+  const bool ok = tok >= 0 && tok < vocab;
+  const T* row = table + (long long)(ok ? tok : 0) * width;
+  float* dst = out + (long long)i * width;
+  const int pieces = width / VEC;
+  for (int p0 = threadIdx.x; p0 < pieces; p0 += 4 * blockDim.x) {
+    Piece v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = p0 + j * blockDim.x;
+      if (p < pieces && ok) v[j] = *reinterpret_cast<const Piece*>(row + p * VEC);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = p0 + j * blockDim.x;
+      if (p >= pieces) continue;
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        float4 o = ok ? make_float4(to_f32<T>(v[j].v[e]), to_f32<T>(v[j].v[e + 1]), to_f32<T>(v[j].v[e + 2]), to_f32<T>(v[j].v[e + 3]))
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(dst + p * VEC + e) = o;
+      }
+    }
+  }
+}
+
 HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, const int* slot_of_token,
                         const int* feedback, float* out, int n, int width, int vocab, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d vocab=%d", n, width, vocab);
   int threads = width >= 256 ? 256 : 64;
-  if (dtype == HFEE_F32)
-    hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
-  else if (dtype == HFEE_BF16)
-    hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
-  else
+  const int vec = dtype == HFEE_F32 ? 4 : 8;
+  const bool vector = width % vec == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (dtype == HFEE_F32) {
+    if (vector) hfee_launch(embed_vec_kernel<float, 4>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
+    else hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
+  } else if (dtype == HFEE_BF16) {
+    if (vector) hfee_launch(embed_vec_kernel<__nv_bfloat16, 8>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
+    else hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
+  } else {
     return hfee_fail(HFEE_ERR_ARG, "embed: unknown dtype %d", dtype);
+  }
   return hfee_check_launch("embed");
 }
 
@@ -70,16 +112,90 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   }
 }
 
+// The same for widths that are multiples of 4 with 16-byte accesses.  A thread owns the pieces
+// tid, tid + THREADS, ...; it requests NCH of them before it uses the first (a loop of load-then-use
+// would pay one memory round trip per piece), the scales even before the wait on the previous
+// kernel, and a row of at most THREADS * 4 * NCH values stays in registers between the two passes.
+template <typename TOut, int THREADS, int NCH>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                   TOut* __restrict__ out, int width, float eps, int add_unit) {
+  constexpr int SPAN = THREADS * 4 * NCH;
+  __shared__ float partial[THREADS / 32];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const bool single = width <= SPAN;
+  float4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (tid + j * THREADS) * 4;
+    wv[j] = c < width ? __ldg(reinterpret_cast<const float4*>(w + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int src_row = rows ? rows[r] : r;                 // host-written, like the batch layout
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* xr = x + (long long)src_row * width;
+  float4 xv[NCH];
+  float ss = 0.f;
+  for (int base = 0; base < width; base += SPAN) {
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = base + (tid + j * THREADS) * 4;
+      xv[j] = c < width ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      ss = fmaf(xv[j].x, xv[j].x, ss); ss = fmaf(xv[j].y, xv[j].y, ss);
+      ss = fmaf(xv[j].z, xv[j].z, ss); ss = fmaf(xv[j].w, xv[j].w, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) partial[tid >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) total += partial[i];
+  const float scale = 1.0f / sqrtf(total / (float)width + eps);
+  TOut* dst = out + (long long)r * width;
+  for (int base = 0; base < width; base += SPAN) {
+    if (!single) {
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int c = base + (tid + j * THREADS) * 4;
+        xv[j] = c < width ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        wv[j] = c < width ? __ldg(reinterpret_cast<const float4*>(w + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = base + (tid + j * THREADS) * 4;
+      if (c >= width) continue;
+      float4 g = wv[j];
+      if (add_unit) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+      const float o0 = xv[j].x * scale * g.x, o1 = xv[j].y * scale * g.y, o2 = xv[j].z * scale * g.z, o3 = xv[j].w * scale * g.w;
+      if constexpr (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4*>(dst + c) = make_float4(o0, o1, o2, o3);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+        *reinterpret_cast<uint2*>(dst + c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      }
+    }
+  }
+}
+
 HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
                           int n, int width, float eps, int add_unit, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0, "rmsnorm: bad sizes n=%d width=%d", n, width);
-  if (out_dtype == HFEE_F32)
-    hfee_launch(rmsnorm_kernel<float, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
-  else if (out_dtype == HFEE_BF16)
-    hfee_launch(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
-  else
+  const bool vector = width % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (out_dtype == HFEE_F32) {
+    if (vector) hfee_launch(rmsnorm_vec_kernel<float, 256, 4>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
+    else hfee_launch(rmsnorm_kernel<float, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
+  } else if (out_dtype == HFEE_BF16) {
+    if (vector) hfee_launch(rmsnorm_vec_kernel<__nv_bfloat16, 256, 4>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
+    else hfee_launch(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
+  } else {
     return hfee_fail(HFEE_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
+  }
   return hfee_check_launch("rmsnorm");
 }
 

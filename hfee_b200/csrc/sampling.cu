@@ -99,9 +99,17 @@ argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int 
   int begin = min(V, ch * per), end = min(V, begin + per);
   float best = -INFINITY;
   int best_i = V;
-  for (int c = begin + tid; c < end; c += THREADS) {
-    float v = row[c];
-    if (best_i == V || v > best) { best = v; best_i = c; }      // ascending c: the first maximum stays
+  // eight loads are requested before the first comparison needs one: a loop of load-then-compare
+  // would pay one memory round trip per element
+  for (int c0 = begin + tid; c0 < end; c0 += 8 * THREADS) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = c0 + j * THREADS < end ? row[c0 + j * THREADS] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j * THREADS;
+      if (c < end && (best_i == V || v[j] > best)) { best = v[j]; best_i = c; }      // ascending c: the first maximum stays
+    }
   }
   s_val[tid] = best;
   s_idx[tid] = best_i;
@@ -123,19 +131,34 @@ argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int 
   }
 }
 
-__global__ void argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out,
-                                     const int* __restrict__ slots, int* __restrict__ feedback) {
+__global__ void __launch_bounds__(32)
+argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __restrict__ out,
+                     const int* __restrict__ slots, int* __restrict__ feedback) {
   pdl_wait();
   pdl_launch_dependents();
-  int r = blockIdx.x;
-  if (threadIdx.x != 0) return;
+  // one warp per row: lane l takes chunks l, l+32, ... (four requested at a time), then the lanes'
+  // winners are compared; the larger value wins, on a tie the lower index (= the earlier chunk)
+  const int r = blockIdx.x, lane = threadIdx.x;
+  const float2* row = reinterpret_cast<const float2*>(part) + (long long)r * chunks;
   float best = -INFINITY;
   int best_i = V;
-  for (int ch = 0; ch < chunks; ++ch) {
-    float v = part[((long long)r * chunks + ch) * 2];
-    int i = __float_as_int(part[((long long)r * chunks + ch) * 2 + 1]);
-    if (i < V && (best_i == V || v > best)) { best = v; best_i = i; }   // chunks ascend: ties keep the first
+  for (int c0 = lane; c0 < chunks; c0 += 4 * 32) {
+    float2 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = c0 + j * 32 < chunks ? row[c0 + j * 32] : make_float2(0.f, __int_as_float(V));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = __float_as_int(v[j].y);
+      if (i < V && (best_i == V || v[j].x > best)) { best = v[j].x; best_i = i; }   // chunks ascend: ties keep the first
+    }
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (i2 < V && (best_i == V || v2 > best || (v2 == best && i2 < best_i))) { best = v2; best_i = i2; }
+  }
+  if (lane != 0) return;
   out[r] = best_i;
   if (feedback) feedback[slots[r]] = best_i;      // kept on the device for the request's next step
 }
