@@ -36,7 +36,57 @@ struct AttnParams {
   int num_splits;
   float* part_o;               // [(token*heads + head)*num_splits + split][HD]
   float* part_ml;              // [...][2] = (max in log2 units, sum)
+  // Fused rotary + cache write (decode steps with one new token per request): q is unused;
+  // queries, the new key and the new value are taken from the projection rows
+  // [q heads | k heads | v heads], rotated here, and the new key/value are also written to the cache.
+  const __nv_bfloat16* rope_qkv; int ld_qkv;
+  const float2* rope_cs;       // [token][rope_dim/2] (cos, sin); null: no rotation
+  int rope_dim, rope_interleaved;
+  __nv_bfloat16* k_write; __nv_bfloat16* v_write;      // the pools, writable; null: this run only reads the cache
 };
+
+// Rotates the 16-byte piece of a head that starts at dim `a` (a multiple of 8): pairs (i, i + half)
+// when `interleaved` is 0, (2i, 2i + 1) otherwise; dims at or above rope_dim pass through.  With
+// half-split pairing the piece at `a` < half is rotated together with its partner at a + half
+// (returns 2: y0 belongs at a, y1 at a + half); the partner piece itself returns 0 (nothing to
+// store); every other piece returns 1 (y0 at a).  Same arithmetic as the rotary kernel:
+// internal/llm/forward.go:181-196.
+__device__ __forceinline__ int rope_piece(const __nv_bfloat16* head, const float2* t, int a, int rope_dim,
+                                          int interleaved, uint4& y0, uint4& y1) {
+  const int half = rope_dim / 2;
+  if (t == nullptr || a >= rope_dim) {
+    y0 = *reinterpret_cast<const uint4*>(head + a);
+    return 1;
+  }
+  union Piece { uint4 u; __nv_bfloat16 v[8]; };
+  if (interleaved) {
+    Piece x, y;
+    x.u = *reinterpret_cast<const uint4*>(head + a);
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const float2 c = t[(a + e) / 2];
+      const float x0 = __bfloat162float(x.v[e]), x1 = __bfloat162float(x.v[e + 1]);
+      y.v[e] = __float2bfloat16_rn(x0 * c.x - x1 * c.y);
+      y.v[e + 1] = __float2bfloat16_rn(x0 * c.y + x1 * c.x);
+    }
+    y0 = y.u;
+    return 1;
+  }
+  if (a >= half) return 0;
+  Piece x0, x1, o0, o1;
+  x0.u = *reinterpret_cast<const uint4*>(head + a);
+  x1.u = *reinterpret_cast<const uint4*>(head + a + half);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float2 c = t[a + e];
+    const float u = __bfloat162float(x0.v[e]), v = __bfloat162float(x1.v[e]);
+    o0.v[e] = __float2bfloat16_rn(u * c.x - v * c.y);
+    o1.v[e] = __float2bfloat16_rn(u * c.y + v * c.x);
+  }
+  y0 = o0.u;
+  y1 = o1.u;
+  return 2;
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -194,14 +244,44 @@ attention_mma_kernel(AttnParams p) {
 
   // ---- stage Q (rows beyond rows_used are zero) with plain loads: it becomes visible with the
   // first block's barrier and belongs to no cp.async group
+  const bool fused_rope = KSPLIT && p.rope_qkv != nullptr;
+  const int rope_half = p.rope_dim / 2;
   for (int idx = tid; idx < ROWS * CHUNKS; idx += THREADS) {
     int row = idx / CHUNKS, ch = idx % CHUNKS;
-    uint4 v = make_uint4(0, 0, 0, 0);
+    uint4 v = make_uint4(0, 0, 0, 0), v2 = v;
+    int pieces = 1;
     if (row < rows_used) {
       int t = t_first + row / p.group, hg = row % p.group;
-      v = *reinterpret_cast<const uint4*>(p.q + (long long)(tok0 + t) * p.ld_q + (long long)(kvh * p.group + hg) * HD + ch * 8);
+      if (fused_rope) {
+        const __nv_bfloat16* head = p.rope_qkv + (long long)(tok0 + t) * p.ld_qkv + (long long)(kvh * p.group + hg) * HD;
+        const float2* tab = p.rope_cs ? p.rope_cs + (long long)(tok0 + t) * rope_half : nullptr;
+        pieces = rope_piece(head, tab, ch * 8, p.rope_dim, p.rope_interleaved, v, v2);
+      } else {
+        v = *reinterpret_cast<const uint4*>(p.q + (long long)(tok0 + t) * p.ld_q + (long long)(kvh * p.group + hg) * HD + ch * 8);
+      }
     }
-    *reinterpret_cast<uint4*>(q_s + row * PITCH + ch * 8) = v;
+    if (pieces >= 1) *reinterpret_cast<uint4*>(q_s + row * PITCH + ch * 8) = v;
+    if (pieces == 2) *reinterpret_cast<uint4*>(q_s + row * PITCH + ch * 8 + rope_half) = v2;
+  }
+  // The new token's key (rotated) and value: held in registers by the first threads of the CTA whose
+  // key range ends at the new position, written to the cache now and into the shared-memory tile
+  // once that block's copy from the cache (which holds nothing valid for this row yet) has landed.
+  const bool patch_cta = fused_rope && p.k_write != nullptr && b_lo <= b_hi && pos_last / BLOCK_N == b_hi;
+  uint4 new_k0 = make_uint4(0, 0, 0, 0), new_k1 = new_k0, new_v = new_k0;
+  int new_k_pieces = 0;
+  if (patch_cta && tid < 2 * CHUNKS) {
+    const __nv_bfloat16* row = p.rope_qkv + (long long)tok0 * p.ld_qkv;
+    const long long at = paged_offset(p.cache, slot, pos_last, kvh);
+    if (tid < CHUNKS) {
+      const float2* tab = p.rope_cs ? p.rope_cs + (long long)tok0 * rope_half : nullptr;
+      new_k_pieces = rope_piece(row + (long long)(p.heads + kvh) * HD, tab, tid * 8, p.rope_dim, p.rope_interleaved, new_k0, new_k1);
+      if (new_k_pieces >= 1) *reinterpret_cast<uint4*>(p.k_write + at + tid * 8) = new_k0;
+      if (new_k_pieces == 2) *reinterpret_cast<uint4*>(p.k_write + at + tid * 8 + rope_half) = new_k1;
+    } else {
+      const int ch = tid - CHUNKS;
+      new_v = *reinterpret_cast<const uint4*>(row + (long long)(p.heads + p.heads / p.group + kvh) * HD + ch * 8);
+      *reinterpret_cast<uint4*>(p.v_write + at + ch * 8) = new_v;
+    }
   }
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
@@ -217,6 +297,17 @@ attention_mma_kernel(AttnParams p) {
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
     __syncthreads();
+    if (patch_cta && b == b_hi) {                       // CTA-uniform
+      const int r_new = pos_last % BLOCK_N;
+      if (tid < CHUNKS) {
+        __nv_bfloat16* dst = k_s + (stage * BLOCK_N + r_new) * PITCH + tid * 8;
+        if (new_k_pieces >= 1) *reinterpret_cast<uint4*>(dst) = new_k0;
+        if (new_k_pieces == 2) *reinterpret_cast<uint4*>(dst + rope_half) = new_k1;
+      } else if (tid < 2 * CHUNKS) {
+        *reinterpret_cast<uint4*>(v_s + (stage * BLOCK_N + r_new) * PITCH + (tid - CHUNKS) * 8) = new_v;
+      }
+      __syncthreads();
+    }
 
     const __nv_bfloat16* kt = k_s + stage * BLOCK_N * PITCH;
     const __nv_bfloat16* vt = v_s + stage * BLOCK_N * PITCH;
@@ -476,18 +567,24 @@ HFEE_API long long hfee_attention_mma_scratch_floats(int n_tokens, int heads, in
 
 // max_new: most new tokens of any request in the batch.  num_splits > 1 needs max_new * group <= rows
 // of one tile and `scratch`.  Returns HFEE_ERR_ARG for head sizes or groups it does not take.
-HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, const void* v_pool,
-                                const int* block_table, int max_pages, int page_size, const int* cu_tokens,
-                                const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
-                                int requests, int max_new, int heads, int kv_heads, int head_dim, float scale,
-                                int window, int num_splits, float* scratch, cudaStream_t stream) {
+namespace {
+struct RopeFusion {
+  const void* qkv; int ld_qkv; const float* cs; int rope_dim; int interleaved; void* k_write; void* v_write;
+};
+
+int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                       const int* block_table, int max_pages, int page_size, const int* cu_tokens,
+                       const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
+                       int requests, int max_new, int heads, int kv_heads, int head_dim, float scale,
+                       int window, int num_splits, float* scratch, const RopeFusion* rope, cudaStream_t stream) {
   if (n_tokens == 0 || requests == 0) return HFEE_OK;
   HFEE_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
                "attention_mma: head_dim %d must be a multiple of 16 in 16..256", head_dim);
   HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention_mma: heads %d / kv_heads %d", heads, kv_heads);
   int group = heads / kv_heads;
   HFEE_REQUIRE(group <= 64, "attention_mma: %d query heads per kv head exceed 64", group);
-  HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 2 == 0 && ((uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
+  HFEE_REQUIRE(ld_o % 2 == 0, "attention_mma: the output's leading dimension must be even");
+  HFEE_REQUIRE(rope != nullptr || (ld_q % 8 == 0 && (uintptr_t)q % 16 == 0), "attention_mma: q must be 16-byte aligned with ld %% 8 == 0");
   HFEE_REQUIRE(requests <= 65535, "attention_mma: too many requests for one grid");
   HFEE_REQUIRE(max_new > 0 && num_splits >= 1 && num_splits <= 32, "attention_mma: num_splits must be in 1..32");
   // when 16 rows hold every request's new tokens (decode) the warps split the keys instead
@@ -512,6 +609,20 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   p.window = window; p.tokens_per_tile = tokens_per_tile; p.num_splits = num_splits;
   p.part_o = scratch;
   p.part_ml = scratch ? scratch + (long long)n_tokens * heads * num_splits * head_dim : nullptr;
+  p.rope_qkv = nullptr; p.ld_qkv = 0; p.rope_cs = nullptr; p.rope_dim = 0; p.rope_interleaved = 0;
+  p.k_write = nullptr; p.v_write = nullptr;
+  if (rope != nullptr) {
+    HFEE_REQUIRE(ksplit && max_new == 1, "attention_mma: rotary fusion is for decode steps of one token per request");
+    HFEE_REQUIRE(rope->qkv != nullptr && (uintptr_t)rope->qkv % 16 == 0 && rope->ld_qkv % 8 == 0 &&
+                 rope->ld_qkv >= (heads + (rope->k_write ? 2 * kv_heads : 0)) * head_dim,
+                 "attention_mma: the projection rows must be 16-byte aligned, ld %% 8 == 0, and hold q, k and v heads");
+    HFEE_REQUIRE(rope->rope_dim >= 0 && rope->rope_dim <= head_dim && rope->rope_dim % 16 == 0,
+                 "attention_mma: rotary fusion needs rope_dim %% 16 == 0 and at most head_dim, got %d", rope->rope_dim);
+    HFEE_REQUIRE((rope->k_write == nullptr) == (rope->v_write == nullptr), "attention_mma: key and value pools go together");
+    p.rope_qkv = (const __nv_bfloat16*)rope->qkv; p.ld_qkv = rope->ld_qkv;
+    p.rope_cs = (const float2*)rope->cs; p.rope_dim = rope->rope_dim; p.rope_interleaved = rope->interleaved;
+    p.k_write = (__nv_bfloat16*)rope->k_write; p.v_write = (__nv_bfloat16*)rope->v_write;
+  }
   int rc;
   switch (head_dim) {
 #define HFEE_CASE(D) case D: rc = dispatch_mode<D>(p, ksplit, q_tiles, kv_heads, requests, stream); break;
@@ -525,6 +636,37 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   hfee_launch(attention_combine_kernel, dim3((unsigned)((pairs + COMBINE_WARPS - 1) / COMBINE_WARPS)),
               dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits, pairs);
   return hfee_check_launch("attention_combine");
+}
+}  // namespace
+
+// q [n_tokens, ld_q], out [n_tokens, ld_o]: bfloat16; pools [num_pages, kv_heads, page_size, head_dim].
+// num_splits > 1 (only when max_new * group <= 16) needs `scratch` of
+// n_tokens * heads * num_splits * (head_dim + 2) floats and launches the combine kernel too.
+HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                const int* block_table, int max_pages, int page_size, const int* cu_tokens,
+                                const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
+                                int requests, int max_new, int heads, int kv_heads, int head_dim, float scale,
+                                int window, int num_splits, float* scratch, cudaStream_t stream) {
+  return attention_mma_impl(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots, context_before,
+                            out, ld_o, n_tokens, requests, max_new, heads, kv_heads, head_dim, scale, window, num_splits,
+                            scratch, nullptr, stream);
+}
+
+// A decode step (one new token per request) with the rotary kernel's work done inside: queries,
+// the new key and the new value come from the projection rows `qkv` [n_tokens, ld_qkv] =
+// [q heads | k heads | v heads]; `cs` [n_tokens, rope_dim/2] holds (cos, sin) pairs (null: no
+// rotation); the rotated key and the value are written to the cache pages of (slot, position)
+// unless `write_cache` is 0 (a run that reads another run's cache: then qkv holds q heads only).
+HFEE_API int hfee_attention_mma_rope(const void* qkv, int ld_qkv, const float* cs, int rope_dim, int interleaved,
+                                     int write_cache, void* k_pool, void* v_pool, const int* block_table, int max_pages,
+                                     int page_size, const int* cu_tokens, const int* slots, const int* context_before,
+                                     void* out, int ld_o, int n_tokens, int requests, int heads, int kv_heads,
+                                     int head_dim, float scale, int window, int num_splits, float* scratch,
+                                     cudaStream_t stream) {
+  RopeFusion rope{qkv, ld_qkv, cs, rope_dim, interleaved, write_cache ? k_pool : nullptr, write_cache ? v_pool : nullptr};
+  return attention_mma_impl(nullptr, 0, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots,
+                            context_before, out, ld_o, n_tokens, requests, 1, heads, kv_heads, head_dim, scale, window,
+                            num_splits, scratch, &rope, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "hfee_attention_tc": [_P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "hfee_attention_tc_supports": [_I, _I, _I, _I],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "hfee_attention_mma_rope": [_P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -421,8 +422,11 @@ MAX_SPLITS = 32
 
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
     """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
-    every SM the three CTAs it can hold at head size 64, at least two key blocks of 64 each."""
-    want = 3 * SM_COUNT // max(1, requests * kv_heads)
+    every SM the three CTAs it can hold at head size 64, and at least four even when the batch
+    alone would fill the GPU (shorter CTAs balance better and keep more loads in flight: measured
+    at 2,048 keys, batch 32: 41.8 us unsplit, 33.4 us with four), but at least two key blocks of
+    64 each."""
+    want = max(4, 3 * SM_COUNT // max(1, requests * kv_heads))
     return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 
@@ -497,6 +501,50 @@ def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_o
     else:
         attention_simt(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
                        head_dim, scale, window)
+
+
+# A decode step of one token per request can do the rotary kernel's work inside the attention
+# kernel (one launch less per layer).
+FUSE_ROPE_INTO_DECODE_ATTENTION = True
+
+
+def decode_rope_fusable(step, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rope_dim: int,
+                        qkv: torch.Tensor, scratch: Optional[torch.Tensor]) -> bool:
+    """True when :func:`paged_attention_rope` takes this step: bfloat16, one new token per request,
+    a group that fits the 16-row decode tile, rotary pieces of whole 16-byte units."""
+    group = heads // kv_heads
+    return (FUSE_ROPE_INTO_DECODE_ATTENTION and step is not None and dtype == torch.bfloat16
+            and getattr(step, "max_new", 0) == 1 and group <= 16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and rope_dim % 16 == 0 and _rows(qkv, "qkv") % 8 == 0 and qkv.data_ptr() % 16 == 0)
+
+
+def paged_attention_rope(qkv, cs, rope_dim, interleaved, write_cache, k_pool, v_pool, block_table, page_size, out,
+                         heads, kv_heads, head_dim, scale, window, step, scratch) -> None:
+    """Rotary + cache write + attention of a decode step in one kernel (plus the combine kernel when
+    the keys are split): ``qkv`` rows are [q heads | k heads | v heads] ([q heads] when
+    ``write_cache`` is false), ``cs`` the (cos, sin) table of the step or None."""
+    lib = library()
+    for t, what in ((block_table, "block_table"), (step.cu_tokens, "cu_tokens"), (step.slots, "slots"),
+                    (step.context_before, "context_before")):
+        _i32(t, what)
+    assert qkv.dtype == k_pool.dtype == out.dtype == torch.bfloat16 and step.n == step.r
+    assert k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.numel() == step.n * rope_dim)
+    splits = 1
+    if scratch is not None:
+        splits = getattr(step, "attention_splits", None) or attention_splits(
+            step.r, kv_heads, getattr(step, "planning_context", step.max_context))
+        if step.n * heads * splits * (head_dim + 2) > scratch.numel():
+            splits = 1
+    _check(lib.hfee_attention_mma_rope(qkv.data_ptr(), _rows(qkv, "qkv"), _ptr(cs), rope_dim, int(interleaved),
+                                       int(write_cache), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                                       block_table.shape[1], page_size, step.cu_tokens.data_ptr(), step.slots.data_ptr(),
+                                       step.context_before.data_ptr(), out.data_ptr(), _rows(out, "attention out"),
+                                       step.n, step.r, heads, kv_heads, head_dim, float(scale), int(window or 0), splits,
+                                       _ptr(scratch) if splits > 1 else None, _stream()), lib)
+    if splits > 1:
+        count_launches(1)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

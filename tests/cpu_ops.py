@@ -139,3 +139,5 @@ def install(monkeypatch):
     for name in ALL:
         monkeypatch.setattr(ops, name, getattr(me, name))
     monkeypatch.setattr(ops, "ARGMAX_CHUNKS", 1, raising=False)
+    # kernel fusions have no double: the parts take their unfused paths
+    monkeypatch.setattr(ops, "FUSE_ROPE_INTO_DECODE_ATTENTION", False, raising=False)

@@ -173,3 +173,46 @@ def test_window_edge_decides(dtype):
     got = out.double().cpu().reshape(heads, hd)[0]
     assert float((got - b.v[0][inside, 0].double()).abs().max()) < (1e-3 if dtype == torch.float32 else 3e-2)
     assert _err(out, b.reference(scale, window)) < (2e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("heads,kv,hd,page,rope_dim,interleaved", [
+    (32, 8, 64, 64, 64, False), (4, 1, 128, 16, 64, False), (3, 3, 32, 16, 32, True), (16, 1, 16, 32, 16, False),
+    (6, 2, 80, 32, 32, True), (8, 2, 64, 64, 0, False)])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("window", [0, 40])
+def test_decode_attention_with_fused_rotary(heads, kv, hd, page, rope_dim, interleaved, splits, window):
+    """One kernel for rotary + cache write + attention of a decode step gives what the rotary kernel
+    followed by the attention kernel gives, and leaves the same keys and values in the cache; the new
+    token sits at a page's first and last row, at a block's edge and in the middle."""
+    from hfee_b200.kernels import ops
+    before = [0, 63, 64, 1499, 700, 255, 127, 128]
+    b = Batch(torch.bfloat16, heads, kv, hd, page, before, [1] * len(before), seed=11)
+    g = torch.Generator().manual_seed(12)
+    qkv = torch.randn(b.n, (heads + 2 * kv) * hd, generator=g).to(torch.bfloat16).to(DEV)
+    cs = None
+    if rope_dim:
+        ang = torch.rand(b.n, rope_dim // 2, generator=g, dtype=torch.float64) * 6.28
+        cs = torch.stack([torch.cos(ang), torch.sin(ang)], -1).float().contiguous().to(DEV)
+    scale = 1 / math.sqrt(hd)
+    # two copies of the cache: the new positions hold stale values in both before the step
+    kp1, vp1, kp2, vp2 = b.kp.clone(), b.vp.clone(), b.kp.clone(), b.vp.clone()
+    q = torch.empty(b.n, heads * hd, dtype=torch.bfloat16, device=DEV)
+    ops.rope_cache_write(qkv, cs, b.positions, b.slot_of_token, q, kp1, vp1, b.table, page, heads, kv, hd, rope_dim, interleaved)
+    scratch = torch.empty(b.n * heads * max(splits, 1) * (hd + 2), dtype=torch.float32, device=DEV)
+    want = torch.full((b.n, heads * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_mma(q, kp1, vp1, b.table, page, b.cu_tokens, b.slots, b.context_before, want, b.n, b.r, 1, heads, kv, hd,
+                      scale, window, splits, scratch)
+    b.attention_splits = splits
+    got = torch.full_like(want, float("nan"))
+    assert ops.decode_rope_fusable(b, torch.bfloat16, heads, kv, hd, rope_dim, qkv, scratch)
+    ops.paged_attention_rope(qkv, cs, rope_dim, interleaved, True, kp2, vp2, b.table, page, got, heads, kv, hd, scale,
+                             window, b, scratch if splits > 1 else None)
+    torch.cuda.synchronize()
+    assert torch.equal(kp1, kp2) and torch.equal(vp1, vp2)
+    assert torch.equal(got, want)
+    # a run that only reads the cache (another run wrote the new key): queries rotated, cache untouched
+    got2 = torch.full_like(want, float("nan"))
+    kp3, vp3 = kp1.clone(), vp1.clone()
+    ops.paged_attention_rope(qkv[:, :heads * hd], cs, rope_dim, interleaved, False, kp3, vp3, b.table, page, got2, heads,
+                             kv, hd, scale, window, b, scratch if splits > 1 else None)
+    assert torch.equal(got2, want) and torch.equal(kp3, kp1) and torch.equal(vp3, vp1)
