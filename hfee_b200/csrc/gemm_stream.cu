@@ -402,8 +402,8 @@ gemm_stream_rows_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
 // contiguous range of 8-row tiles (the ranges differ by at most one tile, whatever N is); the
 // warps' partial sums of a group of up to 8 tiles meet in shared memory (pass after pass in pass
 // order, then added in warp order: one fixed order whatever M is) and are written 64 columns wide.
-// NORM makes the token fragments on the fly from float32 rows, as in the first kernel above, but
-// once per CTA and pass instead of once per tile.
+// NORM (K of at most one pass) makes the token fragments from float32 rows: the RMS norm fused in
+// front, computed once per CTA from the very loads that fill the fragments.
 constexpr int SL_WARPS = 8;
 constexpr int SL_STEPS = 8;                              // k32 steps per warp and pass
 constexpr int SL_SLICE = SL_STEPS * 32;                  // 256 columns per warp and pass
@@ -416,7 +416,8 @@ __global__ void __launch_bounds__(SL_WARPS * 32, 2)
 gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
                           long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K, NormArgs norm) {
   __shared__ __align__(16) float red[2][SL_WARPS][8][SL_TOKEN_PITCH];
-  __shared__ float inv_rms[8];
+  __shared__ __align__(16) float norm_w[NORM ? SL_PASS : 4];       // NORM: the scales of this pass, staged before the wait
+  __shared__ float sq_part[SL_WARPS][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int n_tiles = (N + 7) / 8;
@@ -446,54 +447,72 @@ gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, co
 
   Unit cur{0, 0, 0};
   load_unit(total > 0, cur, wv[0]);
+  const bool tok_ok = g < M;            // this lane's token: row g of the MMA's A tile; rows 8-15 stay zero
+  const float* xrow = nullptr;
+  if constexpr (NORM) {
+    // NORM covers K <= one pass.  The scales do not come from the previous kernel: warp w stages the
+    // 256 of its columns before the wait.
+#pragma unroll
+    for (int i = 0; i < SL_SLICE / 128; ++i) {
+      const int k = warp * SL_SLICE + (lane + i * 32) * 4;
+      float4 v = k < K ? __ldg((const float4*)(norm.weight + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (norm.add_unit) { v.x += 1.f; v.y += 1.f; v.z += 1.f; v.w += 1.f; }
+      *reinterpret_cast<float4*>(&norm_w[k]) = v;
+    }
+    if (tok_ok) xrow = norm.x + (long long)(norm.rows ? norm.rows[g] : g) * norm.ldx;     // host-written gather
+  }
   pdl_wait();
   pdl_launch_dependents();
 
-  // this lane's token (row g of the MMA's A tile; rows 8-15 stay zero)
-  const bool tok_ok = g < M;
   const __nv_bfloat16* arow = A + (long long)(tok_ok ? g : 0) * lda;
-  const float* xrow = nullptr;
-  float scale = 0.f;
-  if constexpr (NORM) {
-    // 1/rms of token w by warp w: fixed order, so a row's scale does not depend on the batch
-    if (warp < M) {
-      const float* xr = norm.x + (long long)(norm.rows ? norm.rows[warp] : warp) * norm.ldx;
-      float ss = 0.f;
-      for (int k = lane * 4; k < K; k += 128) {
-        float4 v = __ldg((const float4*)(xr + k));
-        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(ss / (float)K + norm.eps);
-    }
-    __syncthreads();
-    if (tok_ok) {
-      xrow = norm.x + (long long)(norm.rows ? norm.rows[g] : g) * norm.ldx;
-      scale = inv_rms[g];
-    }
-  }
   uint4 a_lo[SL_STEPS];
   int a_pass = -1;
+  if constexpr (NORM) {
+    // This lane's 64 values of token g (all requested at once), their squares summed over the quad,
+    // the warps' sums added in warp order: one fixed order whatever the batch is.  Then
+    // a = bf16(x * rsqrt(mean(x^2) + eps) * w), as the norm kernel computes it.
+    const int k0 = warp * SL_SLICE + c * 8;
+    float4 xv[2 * SL_STEPS];
+#pragma unroll
+    for (int u = 0; u < SL_STEPS; ++u) {
+      const int k = k0 + u * 32;
+      const bool ok = tok_ok && k < K;
+      xv[2 * u] = ok ? __ldg((const float4*)(xrow + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      xv[2 * u + 1] = ok ? __ldg((const float4*)(xrow + k + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2 * SL_STEPS; ++i) {
+      ss = fmaf(xv[i].x, xv[i].x, ss); ss = fmaf(xv[i].y, xv[i].y, ss);
+      ss = fmaf(xv[i].z, xv[i].z, ss); ss = fmaf(xv[i].w, xv[i].w, ss);
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    if (c == 0) sq_part[warp][g] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < SL_WARPS; ++w) tot += sq_part[w][g];
+    const float scale = 1.0f / sqrtf(tot / (float)K + norm.eps);
+#pragma unroll
+    for (int u = 0; u < SL_STEPS; ++u) {
+      const int k = k0 + u * 32;
+      if (!tok_ok || k >= K) { a_lo[u] = zero; continue; }
+      const float4 n0 = *reinterpret_cast<const float4*>(&norm_w[k]), n1 = *reinterpret_cast<const float4*>(&norm_w[k + 4]);
+      const float4 x0 = xv[2 * u], x1 = xv[2 * u + 1];
+      a_lo[u].x = pack2(x0.x * scale * n0.x, x0.y * scale * n0.y);
+      a_lo[u].y = pack2(x0.z * scale * n0.z, x0.w * scale * n0.w);
+      a_lo[u].z = pack2(x1.x * scale * n1.x, x1.y * scale * n1.y);
+      a_lo[u].w = pack2(x1.z * scale * n1.z, x1.w * scale * n1.w);
+    }
+    a_pass = 0;
+  }
   auto load_tokens = [&](int pass) {
     const int k0 = pass * SL_PASS + warp * SL_SLICE + c * 8;
 #pragma unroll
     for (int u = 0; u < SL_STEPS; ++u) {
       const int k = k0 + u * 32;
-      if (!tok_ok || k >= K) { a_lo[u] = zero; continue; }
-      if constexpr (NORM) {
-        float4 x0 = __ldg((const float4*)(xrow + k)), x1 = __ldg((const float4*)(xrow + k + 4));
-        float4 n0 = __ldg((const float4*)(norm.weight + k)), n1 = __ldg((const float4*)(norm.weight + k + 4));
-        if (norm.add_unit) {
-          n0.x += 1.f; n0.y += 1.f; n0.z += 1.f; n0.w += 1.f;
-          n1.x += 1.f; n1.y += 1.f; n1.z += 1.f; n1.w += 1.f;
-        }
-        a_lo[u].x = pack2(x0.x * scale * n0.x, x0.y * scale * n0.y);
-        a_lo[u].y = pack2(x0.z * scale * n0.z, x0.w * scale * n0.w);
-        a_lo[u].z = pack2(x1.x * scale * n1.x, x1.y * scale * n1.y);
-        a_lo[u].w = pack2(x1.z * scale * n1.z, x1.w * scale * n1.w);
-      } else {
-        a_lo[u] = __ldg((const uint4*)(arow + k));
-      }
+      a_lo[u] = (tok_ok && k < K) ? __ldg((const uint4*)(arow + k)) : zero;
     }
     a_pass = pass;
   };
@@ -695,6 +714,6 @@ HFEE_API int hfee_gemm_stream_norm(const float* X, long long ldx, const int* row
   HFEE_REQUIRE(ldx % 4 == 0 && ldx >= K && (uintptr_t)X % 16 == 0 && (uintptr_t)norm_weight % 16 == 0,
                "gemm_stream_norm: float32 rows need a leading dimension %% 4 == 0 and 16-byte alignment");
   NormArgs norm{X, ldx, rows, norm_weight, eps, add_unit};
-  if (M <= 8) return launch_slices<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
+  if (M <= 8 && K <= SL_PASS) return launch_slices<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
   return by_tokens<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
 }

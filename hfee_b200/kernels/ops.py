@@ -293,10 +293,12 @@ def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
                                      _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
 
 
-# Norming inside the streaming GEMM saves a launch, but every CTA then reads and norms the float32
-# rows itself after its wait on the previous kernel; measured on B200 at batch 8 the decode step got
-# slower (0.96 -> 1.15 ms), so the fusion is off (0 tokens) and the norm kernel runs on its own.
-FUSE_NORM_MAX_TOKENS = 0
+# Norming inside the streaming GEMM saves a launch, but every CTA then reads the float32 rows (twice
+# the bytes of the normed bfloat16 rows, the same addresses from every SM at the same moment).
+# Measured on B200 in the model: batch 1 gains (0.765 -> 0.737 ms per decode step), batch 8 loses
+# (0.88 -> 0.92 ms); the break-even lies near three tokens.
+FUSE_NORM_MAX_TOKENS = 2
+FUSE_NORM_MAX_WIDTH = 2048      # one pass of the kernel that keeps the tokens in registers
 
 
 def _norm_fusable(inp, w: torch.Tensor) -> bool:
@@ -306,7 +308,7 @@ def _norm_fusable(inp, w: torch.Tensor) -> bool:
     p = inp.fused_params()
     x = inp.source
     return (p is not None and inp.out_dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and inp.n <= STREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and _rows(x, "x") % 4 == 0
+            and inp.n <= STREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and x.shape[1] <= FUSE_NORM_MAX_WIDTH and _rows(x, "x") % 4 == 0
             and _rows(w, "w") % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and p[0].data_ptr() % 16 == 0)
 
