@@ -14,6 +14,16 @@
 // Tiles at the edges rely on TMA's zero fill for loads and on predicates for stores; K may
 // be any multiple of 8 (16-byte row pitch), its tail is zero-filled too.
 //
+// When there are tiles for fewer than half of the SMs (prompt portions of a few hundred tokens)
+// the launch splits the work by K blocks: the (tile, K block) pairs in tile order are cut into one
+// contiguous range per CTA, equal to within one block, a whole number of ranges per tile.  A range
+// that starts inside a tile computes that tile's remaining K blocks first, writes the float32 partial
+// tile to its own slot of a workspace and raises the slot's flag; the CTA whose range holds the tile's
+// first K block computes that part last, adds the partial tiles of the following CTAs in CTA order (a
+// fixed order) and runs the epilogue.  Contributions are therefore written at the start of a CTA's
+// work and consumed at the end of another's; the consumer's wait on the flag is bounded like every
+// other wait, and the last consumer warp clears the flag for the next launch.
+//
 // Every mbarrier wait is bounded: a wait that runs out sets an abort flag that ends all
 // other waits of the CTA, records a code in `status` and lets the CTA free its tensor
 // memory and return.
@@ -28,6 +38,7 @@ constexpr int BM = 128;
 constexpr int TC_THREADS = 320;       // 1 TMA warp, 1 MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
+constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ranges of K blocks
 
 enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
@@ -42,7 +53,8 @@ template <int BN> struct TileCfg {
 template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status) {
+               TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status,
+               float* __restrict__ sk_parts, int* __restrict__ sk_flags) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;
@@ -59,6 +71,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int k_blocks = (K + BK - 1) / BK;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
+  // This CTA's work as a sequence of segments (tile, first K block, end K block): whole tiles
+  // b, b + gridDim.x, ... or, split by K blocks, the range [u_begin, u_end) of (tile, K block) pairs.
+  const bool stream_k = sk_parts != nullptr;
+  const long long total_units = (long long)total_tiles * k_blocks;
+  auto range_begin = [&](long long cta) { return cta * total_units / (long long)gridDim.x; };
+  struct Walk { long long u, u_end; int t, stride, tiles, k_blocks; bool stream_k; };
+  auto walk_start = [&]() {
+    Walk w;
+    w.stream_k = stream_k; w.k_blocks = k_blocks; w.tiles = total_tiles; w.stride = gridDim.x; w.t = blockIdx.x;
+    w.u = stream_k ? range_begin(blockIdx.x) : 0;
+    w.u_end = stream_k ? range_begin((long long)blockIdx.x + 1) : 0;
+    return w;
+  };
+  auto walk_next = [](Walk& w, int& t, int& kb0, int& kb1) {
+    if (w.stream_k) {
+      if (w.u >= w.u_end) return false;
+      t = (int)(w.u / w.k_blocks);
+      kb0 = (int)(w.u - (long long)t * w.k_blocks);
+      const long long left = w.u_end - w.u;
+      kb1 = (long long)(w.k_blocks - kb0) <= left ? w.k_blocks : kb0 + (int)left;
+      w.u += kb1 - kb0;
+      return true;
+    }
+    if (w.t >= w.tiles) return false;
+    t = w.t; kb0 = 0; kb1 = w.k_blocks;
+    w.t += w.stride;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -81,11 +121,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;                           // K blocks issued so far, over all tiles
+      uint32_t it = 0;                           // K blocks issued so far, over all segments
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      Walk w = walk_start();
+      int t, kb0, kb1;
+      while (ok && walk_next(w, t, kb0, kb1)) {
         const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag);
           if (!ok) break;
@@ -101,13 +143,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = make_idesc(BM, BN);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++acc_it) {
+      Walk w = walk_start();
+      int t, kb0, kb1;
+      for (; ok && walk_next(w, t, kb0, kb1); ++acc_it) {
         const uint32_t buf = acc_it & 1u;
         ok = mbar_wait(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, &abort_flag);   // epilogue has drained it
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(&full_bar[s], (it / STAGES) & 1u, &abort_flag);
           if (!ok) break;
@@ -116,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t da = make_desc(a_addr), dw = make_desc(a_addr + Cfg::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)       // 16 bf16 = 32 bytes further along K: +2 in 16-byte units
-            tc_mma(tmem_d, da + 2 * k, dw + 2 * k, idesc, (kb | k) != 0);
+            tc_mma(tmem_d, da + 2 * k, dw + 2 * k, idesc, kb > kb0 || k != 0);
           tc_commit(&empty_bar[s]);
         }
         if (ok) tc_commit(&tmem_full_bar[buf]);
@@ -129,19 +173,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int CHUNKS = BN / 32 / 2;          // 32-column chunks per warp
     uint32_t acc_it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++acc_it) {
+    Walk w = walk_start();
+    int t, kb0, kb1;
+    for (; ok && walk_next(w, t, kb0, kb1); ++acc_it) {
       const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
       const uint32_t buf = acc_it & 1u;
       ok = mbar_wait(&tmem_full_bar[buf], (acc_it >> 1) & 1u, &abort_flag);
       tc_fence_after();
       if (!ok) break;
       const int row = m0 + quad * 32 + lane;
+      // split by K blocks: a segment that lacks the tile's first K block hands its partial tile over;
+      // one that has it but not the last adds the partial tiles of the CTAs after this one
+      const bool contribute = kb0 > 0;
+      int parts = 0;
+      if (kb0 == 0 && kb1 < k_blocks) {
+        const long long tile_end = (long long)(t + 1) * k_blocks;
+        while (parts < SK_MAX_PIECES - 1 && blockIdx.x + parts + 1 < gridDim.x &&
+               range_begin((long long)blockIdx.x + parts + 1) < tile_end) ++parts;
+        for (int pi = 1; pi <= parts && ok; ++pi) {
+          int ready = 0;
+          if (lane == 0) {
+            const volatile int* flag = sk_flags + 2 * (blockIdx.x + pi);
+            for (int spin = 0; spin < (1 << 20) && !ready && !*(volatile int*)&abort_flag; ++spin) {
+              ready = *flag >= EPI_WARPS;
+              if (!ready) __nanosleep(200);
+            }
+            if (!ready) abort_flag = 1;
+          }
+          ok = __shfl_sync(0xffffffffu, ready, 0) != 0;
+        }
+        __threadfence();                          // the partial tiles were written before their flags
+        if (!ok) break;
+      }
+      // partial tiles are stored column by column (element (row, col) at col * 128 + row): a warp's
+      // 32 rows of one column are 128 contiguous bytes
+      float* my_part = contribute ? sk_parts + (long long)blockIdx.x * (BM * BN) + (quad * 32 + lane) : nullptr;
 #pragma unroll 1
       for (int cc = 0; cc < CHUNKS; ++cc) {
         const int ch = half * CHUNKS + cc;
         uint32_t v[32];
         tc_ld32(tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 32), v);
         tc_wait_ld();
+        if (contribute) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) my_part[(ch * 32 + j) * BM] = __uint_as_float(v[j]);
+          continue;
+        }
+        if (parts > 0) {
+          // all the partial tiles' values of this chunk are requested before the first is added
+          const float* src = sk_parts + (long long)(blockIdx.x + 1) * (BM * BN) + (long long)(ch * 32) * BM + (quad * 32 + lane);
+          float x[SK_MAX_PIECES - 1][32];
+#pragma unroll
+          for (int pi = 0; pi < SK_MAX_PIECES - 1; ++pi)
+            if (pi < parts) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) x[pi][j] = __ldcg(src + (long long)pi * (BM * BN) + j * BM);
+            }
+#pragma unroll
+          for (int pi = 0; pi < SK_MAX_PIECES - 1; ++pi)
+            if (pi < parts) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + x[pi][j]);
+            }
+        }
         const int col0 = n0 + ch * 32;
         if (row >= M || col0 >= N) continue;
         if constexpr (EPI == EPI_SWIGLU) {
@@ -213,6 +307,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+      if (contribute) {
+        __threadfence();                          // this warp's part of the partial tile before its flag
+        __syncwarp();
+        if (lane == 0) atomicAdd(sk_flags + 2 * blockIdx.x, 1);
+      } else if (parts > 0) {
+        __syncwarp();
+        if (lane == 0) {
+          for (int pi = 1; pi <= parts; ++pi) {
+            int* flag = sk_flags + 2 * (blockIdx.x + pi);
+            if (atomicAdd(flag + 1, 1) == EPI_WARPS - 1) {          // the last warp to have read it clears the slot
+              flag[0] = 0;
+              flag[1] = 0;
+            }
+          }
+        }
+      }
     }
   }
 
@@ -231,9 +341,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------- host
+// Whether to split by K blocks, and over how many CTAs.  Only when whole tiles would leave at
+// least half of the SMs idle: CTAs that work on one panel of A or W at different K positions lose
+// the sharing of those loads in L2 (measured: with 148 staggered ranges a K block took three times
+// as long), so every tile is cut into the same number of (nearly) equal pieces, which keeps the
+// CTAs of one piece index in step, and tiles that fill most SMs are left whole.
+int plan_stream_k(long long tiles, int k_blocks, int sms, long long workspace_floats, int bn) {
+  if (tiles * 2 > sms || k_blocks < 64) return 0;            // a short K gains less than the hand-over costs
+  long long pieces = sms / tiles < SK_MAX_PIECES ? sms / tiles : SK_MAX_PIECES;
+  while (pieces > 1 && k_blocks / pieces < 8) --pieces;       // at least 8 K blocks per piece
+  const long long ctas = tiles * pieces;
+  if (pieces < 2 || workspace_floats < ctas * (long long)BM * bn) return 0;
+  return (int)ctas;
+}
+
 template <int BN, int EPI, typename TOut>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
-           cudaStream_t stream) {
+           float* workspace, long long workspace_floats, int* flags, cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   static bool configured = false;
   if (!configured) {
@@ -249,24 +373,26 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
     if (sms <= 0) sms = 148;
   }
   long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // one CTA per SM walks the tiles
-  hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, (TOut*)C, ldc, M, N, K, status);
+  const int sk_ctas = (workspace && flags) ? plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, BN) : 0;
+  dim3 grid((unsigned)(sk_ctas ? sk_ctas : (tiles < sms ? tiles : sms)));          // one CTA per SM
+  hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, (TOut*)C, ldc, M, N, K, status,
+              sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr);
   return hfee_check_launch("gemm_tcgen05");
 }
 
 template <int BN>
 int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int out_dtype, int epilogue, int M,
-             int N, int K, int* status, cudaStream_t stream) {
+             int N, int K, int* status, float* ws, long long ws_floats, int* flags, cudaStream_t stream) {
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: accumulate needs a float32 output");
-    return launch<BN, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, stream);
+    return launch<BN, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   }
   if (epilogue == EPI_SWIGLU) {
     if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue writes bfloat16");
-    return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+    return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   }
-  if (out_dtype == HFEE_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
-  return launch<BN, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
+  if (out_dtype == HFEE_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
+  return launch<BN, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
 }
 
 }  // namespace
@@ -274,9 +400,12 @@ int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ld
 // A, W: bfloat16, 16-byte aligned, leading dimensions multiples of 8.  epilogue: 0 store, 1 accumulate
 // into float32 C, 2 SwiGLU over W rows interleaved [4 gate | 4 up] (C is [M, N/2] bfloat16).
 // `status` (device int, may be null) is set to 1 if a CTA gave up waiting.  block_n: 128 or 256.
+// `workspace` (float32, 16-byte aligned, may be null) and `flags` (2 ints per SM, zero before the
+// first use; every launch leaves them zero) allow the split by K blocks: it is used when it pays and
+// the workspace holds one 128 x block_n tile per CTA.
 HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
                                int out_dtype, int epilogue, int M, int N, int K, int block_n, int* status,
-                               cudaStream_t stream) {
+                               float* workspace, long long workspace_floats, int* flags, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "gemm_tcgen05: K=%d must be a positive multiple of 8", K);
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
@@ -292,6 +421,17 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   if (rc != HFEE_OK) return rc;
   rc = make_map(&mw, W, N, K, ldw, block_n);
   if (rc != HFEE_OK) return rc;
-  if (block_n == 256) return dispatch<256>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, stream);
-  return dispatch<128>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, stream);
+  HFEE_REQUIRE((uintptr_t)workspace % 16 == 0, "gemm_tcgen05: the workspace must be 16-byte aligned");
+  if (block_n == 256) return dispatch<256>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
+  return dispatch<128>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
+}
+
+// How many CTAs hfee_gemm_tcgen05 would split this shape's K blocks among (0: whole tiles per CTA).
+HFEE_API int hfee_gemm_tcgen05_stream_k(int M, int N, int K, int block_n, long long workspace_floats) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  long long tiles = (long long)((M + BM - 1) / BM) * ((N + block_n - 1) / block_n);
+  return plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, block_n);
 }

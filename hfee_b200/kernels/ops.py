@@ -33,7 +33,8 @@ _SIGNATURES = {
     "hfee_swiglu": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_gemm_stream_norm": [_P, _L, _P, _P, _F, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
-    "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+    "hfee_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _L, _P, _P],
+    "hfee_gemm_tcgen05_stream_k": [_I, _I, _I, _I, _L],
     "hfee_gemm_skinny": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _P],
     "hfee_gemm_skinny_splits": [_I, _I, _I, _L],
     "hfee_attention_tc": [_P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -257,7 +258,7 @@ def _tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE,
-                 block_n: Optional[int] = None) -> None:
+                 block_n: Optional[int] = None, stream_k: Optional[bool] = None) -> None:
     """out (+)= a @ w.T with tcgen05.mma tiles of 128 x block_n fed by TMA (bfloat16 in, float32
     accumulation in tensor memory).  Epilogues as in :func:`gemm_stream`."""
     lib = library()
@@ -271,9 +272,27 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         # at M = N = 2048 (128 wide tiles on 148 SMs): K = 8192 takes 61 us wide, 95 us narrow.
         tiles_256 = -(-m // 128) * -(-n // 256)
         block_n = 256 if tiles_256 >= 96 else 128
+    if stream_k is None:
+        stream_k = USE_STREAM_K
+    ws, flags = _stream_k_workspace() if stream_k else (None, None)
     _check(lib.hfee_gemm_tcgen05(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                  _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, block_n,
-                                 _status().data_ptr(), _stream()), lib)
+                                 _status().data_ptr(), _ptr(ws), ws.numel() if ws is not None else 0, _ptr(flags),
+                                 _stream()), lib)
+
+
+USE_STREAM_K = True
+_STREAM_K_WS = None
+
+
+def _stream_k_workspace():
+    """One float32 tile of 128 x 256 per SM for the partial tiles of products split by K blocks, and
+    two flag words per SM (zero at the start; every launch leaves them zero).  Made once, 19 MiB."""
+    global _STREAM_K_WS
+    if _STREAM_K_WS is None:
+        _STREAM_K_WS = (torch.empty(SM_COUNT * 128 * 256, dtype=torch.float32, device="cuda"),
+                        torch.zeros(2 * SM_COUNT, dtype=torch.int32, device="cuda"))
+    return _STREAM_K_WS
 
 
 def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,

@@ -45,7 +45,7 @@ def test_store_and_accumulate(m, n, k, block_n):
 
 
 @pytest.mark.parametrize("block_n", [128, 256])
-@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (300, 172, 96), (2048, 8192, 2048), (70, 1000, 264)])
+@pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (300, 172, 96), (2048, 8192, 2048), (70, 1000, 264), (200, 1000, 4096)])
 def test_swiglu_epilogue(m, inner, k, block_n):
     from hfee_b200.kernels import ops
     g = torch.Generator().manual_seed(inner)
@@ -58,6 +58,37 @@ def test_swiglu_epilogue(m, inner, k, block_n):
     ops.check_status()
     gd, ud = a.double().cpu() @ gate.double().t(), a.double().cpu() @ up.double().t()
     assert _err(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 2048, 8192), (256, 2048, 8192), (333, 1000, 8192), (130, 300, 4104), (1000, 500, 6000)])
+def test_split_by_k_blocks_matches_whole_tiles(m, n, k):
+    """Shapes with tiles for less than half of the SMs and a long K are split by K blocks among the
+    CTAs (partial tiles through a workspace, added in CTA order): same result as whole tiles up to the rounding of
+    the partial sums, the same bits from launch to launch, and the flags are left clear."""
+    from hfee_b200.kernels import ops
+    lib = ops.library()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    ref = a.double().cpu() @ w.double().cpu().t()
+    ws, flags = ops._stream_k_workspace()
+    assert lib.hfee_gemm_tcgen05_stream_k(m, n, k, 256, ws.numel()) > 0      # these shapes are split
+    whole = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(a, w, whole, ops.EPI_STORE, 256, stream_k=False)
+    outs = []
+    for _ in range(3):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_tcgen05(a, w, out, ops.EPI_STORE, 256, stream_k=True)
+        ops.check_status()
+        assert int(flags.abs().sum()) == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert _err(outs[0], ref) < _f32_tol(k) and _err(whole, ref) < _f32_tol(k)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_tcgen05(a, w, acc, ops.EPI_ACCUM, 256, stream_k=True)
+    ops.check_status()
+    assert _err(acc, base.double().cpu() + ref) < _f32_tol(k)
 
 
 def test_strided_operands():
