@@ -70,8 +70,14 @@ __device__ __forceinline__ void write_columns(const uint32_t (&v)[COLS], int tok
     for (int j = 0; j < COLS; ++j) {
       float gate = __uint_as_float(v[j]);
       float up = __shfl_down_sync(0xffffffffu, gate, 4);
-      if (writer && tok0 + j < a.M)
-        C[(long long)(tok0 + j) * a.ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+      if (writer && tok0 + j < a.M) {
+        // a bfloat16 result does not need the exact exponential and division (the large-tile kernel
+        // computes it the same way)
+        float h;
+        if constexpr (sizeof(TOut) == 2) h = __fdividef(gate, 1.f + __expf(-gate)) * up;
+        else h = gate / (1.f + expf(-gate)) * up;
+        C[(long long)(tok0 + j) * a.ldc + col] = from_f32<TOut>(h);
+      }
     }
   } else {
     if (!row_ok) return;
