@@ -47,12 +47,14 @@ template <int BN> struct TileCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int W_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;      // + slack to align the base to 1024
+  static constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;        // accumulate epilogue: a 32 x 32 float chunk per warp
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;      // + slack to align the base to 1024
 };
 
 template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_c, int reduce_by_tma,
                TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status,
                float* __restrict__ sk_parts, int* __restrict__ sk_flags) {
   using Cfg = TileCfg<BN>;
@@ -67,6 +69,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ int abort_flag;
 
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* epi_stage = tiles + STAGES * Cfg::STAGE_BYTES;      // 1024-aligned: the tiles are whole KBs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = (K + BK - 1) / BK;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -237,6 +240,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
         const int col0 = n0 + ch * 32;
+        if constexpr (EPI == EPI_ACCUM) {
+          if (reduce_by_tma) {
+            // The chunk goes to shared memory (thread = row, 128 bytes, in the 128-byte swizzle the
+            // tensor map of C expects) and from there into C by a bulk tensor reduction: the addition
+            // happens in the memory system, nothing of C is read here, and rows or columns beyond the
+            // matrix are clipped by the copy.
+            const int row0 = m0 + quad * 32;
+            if (row0 >= M || col0 >= N) continue;                      // the same for the whole warp
+            unsigned char* cs = epi_stage + (warp - 2) * 4096;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous chunk has left the buffer
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(cs + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(reinterpret_cast<uint64_t>(&map_c)), "r"(col0), "r"(row0), "r"(smem_u32(cs)) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            continue;
+          }
+        }
         if (row >= M || col0 >= N) continue;
         if constexpr (EPI == EPI_SWIGLU) {
           // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col/2
@@ -326,6 +354,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
+  if constexpr (EPI == EPI_ACCUM) {
+    // bulk reductions of this thread are complete (not merely read out of shared memory) before the CTA ends
+    if (reduce_by_tma && warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
   tc_fence_before();
   __syncthreads();
   if (abort_flag) {
@@ -355,10 +387,32 @@ int plan_stream_k(long long tiles, int k_blocks, int sms, long long workspace_fl
   return (int)ctas;
 }
 
+// Tensor map of the float32 output for the bulk reduction of 32 x 32 chunks (128-byte rows, swizzled).
+int make_map_c(CUtensorMap* map, void* base, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+  return HFEE_OK;
+}
+
 template <int BN, int EPI, typename TOut>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
            float* workspace, long long workspace_floats, int* flags, cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
+  // accumulate: by bulk tensor reduction when C can have a tensor map (16-byte aligned base and pitch)
+  CUtensorMap mc = ma;
+  int reduce_by_tma = 0;
+  if (EPI == EPI_ACCUM && (uintptr_t)C % 16 == 0 && ldc % 4 == 0) {
+    int rc = make_map_c(&mc, C, M, N, ldc);
+    if (rc != HFEE_OK) return rc;
+    reduce_by_tma = 1;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
@@ -375,7 +429,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
   long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sk_ctas = (workspace && flags) ? plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, BN) : 0;
   dim3 grid((unsigned)(sk_ctas ? sk_ctas : (tiles < sms ? tiles : sms)));          // one CTA per SM
-  hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, (TOut*)C, ldc, M, N, K, status,
+  hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status,
               sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr);
   return hfee_check_launch("gemm_tcgen05");
 }
