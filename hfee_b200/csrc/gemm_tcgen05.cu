@@ -2,7 +2,7 @@
 // staged in shared memory by TMA (128-byte swizzle, no multicast), tcgen05.mma issued by
 // one thread with the float32 accumulator in tensor memory, tcgen05.ld for the epilogue.
 //
-// The grid is persistent: CTA b computes the 128 x BN tiles (BN = 128 or 256) b, b + gridDim.x,
+// The grid is persistent: CTA b computes the 128 x BN tiles (BN = 128, 192 or 256) b, b + gridDim.x,
 // ... (M tiles fastest, so CTAs running together share a W tile in L2), K in blocks of 64, with
 // two accumulators in tensor memory so that a tile's epilogue overlaps the next tile's MMAs:
 //   warp 0     TMA producer   waits empty[s], arms full[s] with the stage's bytes, issues 2 loads
@@ -43,7 +43,7 @@ constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ra
 enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
 template <int BN> struct TileCfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int STAGES = BN == 128 ? 6 : 4;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int W_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
@@ -59,7 +59,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                float* __restrict__ sk_parts, int* __restrict__ sk_flags) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;
+  constexpr uint32_t TMEM_COLS = ACC_STAGES * BN <= 256 ? 256 : 512;      // a power of two
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -453,7 +453,7 @@ int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ld
 
 // A, W: bfloat16, 16-byte aligned, leading dimensions multiples of 8.  epilogue: 0 store, 1 accumulate
 // into float32 C, 2 SwiGLU over W rows interleaved [4 gate | 4 up] (C is [M, N/2] bfloat16).
-// `status` (device int, may be null) is set to 1 if a CTA gave up waiting.  block_n: 128 or 256.
+// `status` (device int, may be null) is set to 1 if a CTA gave up waiting.  block_n: 128, 192 or 256.
 // `workspace` (float32, 16-byte aligned, may be null) and `flags` (2 ints per SM, zero before the
 // first use; every launch leaves them zero) allow the split by K blocks: it is used when it pays and
 // the workspace holds one 128 x block_n tile per CTA.
@@ -468,7 +468,7 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
   HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_tcgen05: SwiGLU needs N %% 8 == 0, got %d", N);
   HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_tcgen05: ldc=%lld is too small", ldc);
-  HFEE_REQUIRE(block_n == 128 || block_n == 256, "gemm_tcgen05: block_n must be 128 or 256");
+  HFEE_REQUIRE(block_n == 128 || block_n == 192 || block_n == 256, "gemm_tcgen05: block_n must be 128, 192 or 256");
   HFEE_REQUIRE((long long)((M + BM - 1) / BM) * ((N + block_n - 1) / block_n) < (1ll << 31), "gemm_tcgen05: too many tiles");
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
@@ -477,6 +477,7 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   if (rc != HFEE_OK) return rc;
   HFEE_REQUIRE((uintptr_t)workspace % 16 == 0, "gemm_tcgen05: the workspace must be 16-byte aligned");
   if (block_n == 256) return dispatch<256>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
+  if (block_n == 192) return dispatch<192>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
   return dispatch<128>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
 }
 

@@ -22,7 +22,7 @@ SHAPES = [(128, 128, 64), (128, 256, 128), (256, 128, 512), (65, 8, 8), (200, 30
           (1000, 96, 2048), (2048, 3072, 2048), (333, 1000, 8192)]
 
 
-@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("block_n", [128, 192, 256])
 @pytest.mark.parametrize("m,n,k", SHAPES)
 def test_store_and_accumulate(m, n, k, block_n):
     from hfee_b200.kernels import ops
@@ -44,7 +44,7 @@ def test_store_and_accumulate(m, n, k, block_n):
     assert _err(acc, base.double().cpu() + ref) < _f32_tol(k)
 
 
-@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("block_n", [128, 192, 256])
 @pytest.mark.parametrize("m,inner,k", [(128, 64, 64), (300, 172, 96), (2048, 8192, 2048), (70, 1000, 264), (200, 1000, 4096)])
 def test_swiglu_epilogue(m, inner, k, block_n):
     from hfee_b200.kernels import ops
