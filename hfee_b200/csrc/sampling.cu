@@ -163,6 +163,195 @@ argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __r
   if (feedback) feedback[slots[r]] = best_i;      // kept on the device for the request's next step
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The whole chain of hostfog/hfee internal/llm/sampler.go:54-130 on the device, for rows whose
+// top-k is between 1 and CHAIN_MAX_K (a greedy row is the chain with k = 1): repeat penalty over the
+// request's recent tokens (kept in a ring per request slot), the k largest logits in descending
+// order (ties: lower id first), probabilities exp((l - l_max) / T) in float64, top-p and min-p cuts,
+// and the draw r = U * total that walks the kept candidates.
+//
+// Per row eight doubles of parameters: temperature, top_k, top_p, min_p, repeat penalty,
+// repeat_last_n, uniform number, unused.  top_p and min_p arrive rounded to float32, as the
+// reference compares them.
+constexpr int CHAIN_MAX_K = 64;
+constexpr int CHAIN_CHUNK = 2048;          // vocabulary entries one stage-1 block looks at (8 per thread)
+constexpr int CHAIN_PARAMS = 8;
+
+// sampler.go:57-74: every distinct id among the last `repeat_last_n` tokens once; a positive logit
+// is divided by the penalty, another multiplied.  In place.
+__global__ void __launch_bounds__(THREADS)
+chain_penalty_kernel(float* __restrict__ logits, long long ld, int V, const double* __restrict__ params,
+                     const int* __restrict__ slots, const int* __restrict__ history, int cap,
+                     const int* __restrict__ history_len) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ int toks[THREADS];
+  const int r = blockIdx.x, i = threadIdx.x;
+  const float pen = (float)params[r * CHAIN_PARAMS + 4];
+  const int last_n = (int)params[r * CHAIN_PARAMS + 5];
+  if (pen == 1.f || last_n <= 0) return;                       // the same for the whole block
+  const int slot = slots[r], len = history_len[slot];
+  const int cnt = min(min(last_n, len), min(cap, THREADS));
+  if (i < cnt) toks[i] = history[(long long)slot * cap + (len - 1 - i) % cap];
+  __syncthreads();
+  if (i >= cnt) return;
+  const int tok = toks[i];
+  for (int j = 0; j < i; ++j)
+    if (toks[j] == tok) return;                                // a later copy of an id already handled
+  if (tok < 0 || tok >= V) return;
+  float* x = logits + (long long)r * ld + tok;
+  *x = *x > 0.f ? *x / pen : *x * pen;
+}
+
+// One round of "largest remaining value, lowest index on ties" over a block: every thread offers its
+// best, the winner is broadcast.  An offer with index `none` never wins.
+__device__ __forceinline__ void block_best(float& val, int& idx, int none, float* s_val, int* s_idx) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, val, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
+  }
+  __syncthreads();                                             // the previous round's winner has been read
+  if (lane == 0) { s_val[warp] = val; s_idx[warp] = idx; }
+  __syncthreads();
+  val = s_val[0]; idx = s_idx[0];
+#pragma unroll
+  for (int w = 1; w < THREADS / 32; ++w) {
+    const float v2 = s_val[w];
+    const int i2 = s_idx[w];
+    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
+  }
+}
+
+// Stage 1: the k largest of each chunk of a row, in descending order, to cand[(row, chunk)][CHAIN_MAX_K] as
+// (value, id) pairs; unused places hold id V.
+__global__ void __launch_bounds__(THREADS)
+chain_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int chunks, const double* __restrict__ params,
+                    float2* __restrict__ cand) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float s_val[THREADS / 32];
+  __shared__ int s_idx[THREADS / 32];
+  constexpr int NE = CHAIN_CHUNK / THREADS;
+  const int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
+  const double temp = params[r * CHAIN_PARAMS];
+  const int k = temp > 0.0 ? min(max((int)params[r * CHAIN_PARAMS + 1], 1), CHAIN_MAX_K) : 1;
+  const float* row = logits + (long long)r * ld;
+  const int begin = ch * CHAIN_CHUNK;
+  float v[NE];
+  unsigned alive = 0;
+#pragma unroll
+  for (int j = 0; j < NE; ++j) {
+    const int c = begin + tid + j * THREADS;
+    v[j] = c < V ? row[c] : 0.f;
+    if (c < V) alive |= 1u << j;
+  }
+  float2* dst = cand + ((long long)r * chunks + ch) * CHAIN_MAX_K;
+  for (int round = 0; round < k; ++round) {
+    float bv = 0.f;
+    int bj = -1;
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+      if (((alive >> j) & 1u) && (bj < 0 || v[j] > bv)) { bv = v[j]; bj = j; }      // ascending j = ascending id
+    float val = bv;
+    int idx = bj >= 0 ? begin + tid + bj * THREADS : V;
+    const int mine = idx;
+    block_best(val, idx, V, s_val, s_idx);
+    if (idx != V && idx == mine) alive &= ~(1u << bj);
+    if (tid == 0) dst[round] = make_float2(val, __int_as_float(idx));
+  }
+}
+
+// Stage 2: the k largest of a row's candidates, then the chain.  Appends the choice to the request's
+// history ring (when there is one) and stores it in feedback[slot] for the next step's embedding.
+__global__ void __launch_bounds__(THREADS)
+chain_stage2_kernel(const float2* __restrict__ cand, int V, int chunks, const double* __restrict__ params,
+                    const int* __restrict__ slots, int* __restrict__ history, int cap, int* __restrict__ history_len,
+                    int* __restrict__ out, int* __restrict__ feedback) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float s_val[THREADS / 32];
+  __shared__ int s_idx[THREADS / 32];
+  __shared__ float top_val[CHAIN_MAX_K];
+  __shared__ int top_idx[CHAIN_MAX_K];
+  __shared__ double prob[CHAIN_MAX_K];
+  constexpr int NE = 32;                                        // up to 128 chunks x 64 candidates over 256 threads
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const double* pr = params + r * CHAIN_PARAMS;
+  const double temp = pr[0];
+  const int k = temp > 0.0 ? min(max((int)pr[1], 1), CHAIN_MAX_K) : 1;
+  const int total = chunks * k;                                 // candidate e = chunk e / k, place e % k
+  float v[NE];
+  int id[NE];
+#pragma unroll
+  for (int j = 0; j < NE; ++j) {
+    const int e = tid + j * THREADS;
+    id[j] = V;
+    v[j] = 0.f;
+    if (e < total) {
+      const float2 c = cand[((long long)r * chunks + e / k) * CHAIN_MAX_K + e % k];
+      v[j] = c.x;
+      id[j] = __float_as_int(c.y);
+    }
+  }
+  for (int round = 0; round < k; ++round) {
+    float bv = 0.f;
+    int bi = V, bj = -1;
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+      if (id[j] != V && (bi == V || v[j] > bv || (v[j] == bv && id[j] < bi))) { bv = v[j]; bi = id[j]; bj = j; }
+    float val = bv;
+    int idx = bi;
+    block_best(val, idx, V, s_val, s_idx);
+    if (idx != V && idx == bi) id[bj] = V;
+    if (tid == 0) { top_val[round] = val; top_idx[round] = idx; }
+  }
+  __syncthreads();
+  if (temp > 0.0 && tid < k)
+    prob[tid] = top_idx[tid] != V ? exp((double)((top_val[tid] - top_val[0]) / (float)temp)) : 0.0;
+  __syncthreads();
+  if (tid != 0) return;
+  int token = top_idx[0];
+  if (temp > 0.0) {
+    int n = 0;
+    double sum = 0.0;
+    while (n < k && top_idx[n] != V) sum += prob[n++];
+    const double top_p = pr[2], min_p = pr[3];
+    int keep = n;
+    if (top_p > 0.0 && top_p < 1.0) {
+      double cum = 0.0;
+      for (int i = 0; i < n; ++i) {
+        cum += prob[i] / sum;
+        if (cum >= top_p) { keep = i + 1; break; }
+      }
+    }
+    if (min_p > 0.0)
+      for (int i = 1; i < keep; ++i)
+        if (prob[i] / sum < min_p * (prob[0] / sum)) { keep = i; break; }
+    double kept = 0.0;
+    for (int i = 0; i < keep; ++i) kept += prob[i] / sum;
+    double left = pr[6] * kept;
+    token = top_idx[keep - 1];
+    for (int i = 0; i < keep; ++i) {
+      left -= prob[i] / sum;
+      if (left <= 0.0) { token = top_idx[i]; break; }
+    }
+  }
+  out[r] = token;
+  if (slots != nullptr) {
+    const int slot = slots[r];
+    if (feedback != nullptr) feedback[slot] = token;
+    if (history != nullptr) {
+      const int len = history_len[slot];
+      history[(long long)slot * cap + len % cap] = token;
+      history_len[slot] = len + 1;
+    }
+  }
+}
+
 }  // namespace
 
 // scratch: M * chunks * 2 floats.
@@ -185,4 +374,31 @@ HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const 
   HFEE_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures need uniform numbers");
   hfee_launch(sample_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, temperature, uniform, out, slots, feedback);
   return hfee_check_launch("sample");
+}
+
+// The sampling chain on the device for M rows (see chain_stage2_kernel).  `params`: M x 8 doubles.
+// `logits` is changed in place where a row penalises.  `scratch`: M * ceil(V / 2048) * 64 * 2 floats.
+// `history` [slots][cap] int32 with `history_len` [slots] (tokens appended so far): the rings of recent
+// tokens, may be null when no row penalises; `slots` maps rows to request slots (needed with
+// history or feedback).
+HFEE_API int hfee_sample_chain(float* logits, long long ld, int M, int V, const double* params, const int* slots,
+                               int* history, int history_cap, int* history_len, int penalise, float* scratch,
+                               long long scratch_floats, int* out, int* feedback, cudaStream_t stream) {
+  if (M == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && M <= 65535 && V > 0 && ld >= V && params != nullptr && out != nullptr, "sample_chain: bad sizes M=%d V=%d", M, V);
+  const int chunks = (V + CHAIN_CHUNK - 1) / CHAIN_CHUNK;
+  HFEE_REQUIRE(chunks <= 128, "sample_chain: a vocabulary of %d exceeds %d", V, 128 * CHAIN_CHUNK);
+  HFEE_REQUIRE(scratch != nullptr && scratch_floats >= (long long)M * chunks * CHAIN_MAX_K * 2 && (uintptr_t)scratch % 8 == 0,
+               "sample_chain: the scratch must hold %lld floats", (long long)M * chunks * CHAIN_MAX_K * 2);
+  HFEE_REQUIRE((feedback == nullptr && history == nullptr) || slots != nullptr, "sample_chain: feedback and history need the rows' slots");
+  HFEE_REQUIRE(!penalise || (history != nullptr && history_len != nullptr && history_cap > 0 && history_cap <= THREADS),
+               "sample_chain: a repeat penalty needs the history rings (at most %d tokens each)", THREADS);
+  if (penalise)
+    hfee_launch(chain_penalty_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, params, slots, (const int*)history,
+                history_cap, (const int*)history_len);
+  hfee_launch(chain_stage1_kernel, dim3((unsigned)chunks, (unsigned)M), dim3(THREADS), 0, stream, (const float*)logits, ld, V,
+              chunks, params, (float2*)scratch);
+  hfee_launch(chain_stage2_kernel, dim3(M), dim3(THREADS), 0, stream, (const float2*)scratch, V, chunks, params, slots, history,
+              history_cap, history_len, out, feedback);
+  return hfee_check_launch("sample_chain");
 }

@@ -116,7 +116,8 @@ class Engine:
         # When every request samples on the device and nothing needs text, steps are pipelined:
         # the sampled tokens stay on the device for the next step and the host reads them one step
         # late, so planning and launching overlap the GPU's work.
-        if self.pipeline and all(o.device_only and not o.stop for o in options):
+        on_device = all(o.device_only for o in options) or all(o.device_chain for o in options)
+        if self.pipeline and on_device and not any(o.stop for o in options):
             inflight = None
             while not sched.idle or inflight is not None:
                 launched = self.launch_step(sched) if not sched.idle else None
@@ -161,6 +162,10 @@ class Engine:
         handle = None
         if logits is not None:
             who = [e.request for e in plan if e.wants_logits]
+            for r in who:                     # a request's first draw since it was admitted: its recent tokens go to the device
+                if r.options.penalises and not r.ring_loaded:
+                    self.sampler.load_history(r.slot, r.prompt + r.output)
+                    r.ring_loaded = True
             handle = self.sampler.launch(logits, [r.options for r in who], [r.seed for r in who],
                                          [r.draws for r in who], step.logit_slots, self.runner.feedback)
         return sched.update_provisional(plan), handle

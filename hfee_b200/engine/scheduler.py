@@ -55,6 +55,7 @@ class Request:
     slot: Optional[int] = None
     seed: int = 0
     draws: int = 0
+    ring_loaded: bool = False          # the device-side ring of recent tokens holds this request's history
     decoding: bool = False                               # the prompt has been read (evalStart set)
     finished: Optional[str] = None
     order: int = -1                                      # admission sequence number
@@ -209,6 +210,7 @@ class Scheduler:
         req.slot = None
         req.feed = req.prompt + req.output          # recompute everything when re-admitted (rebuilt at admission,
         req.decoding = False                        # when placeholders in the output have been resolved)
+        req.ring_loaded = False
         req.stats.preemptions += 1
         self.preemptions += 1
         self.waiting.appendleft(req)

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P],
+    "hfee_sample_chain": [_P, _L, _I, _I, _P, _P, _P, _I, _P, _I, _P, _L, _P, _P, _P],
 }
 
 
@@ -589,6 +590,38 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
         assert temperature.dtype == torch.float32 and uniform.dtype == torch.float64
     _check(lib.hfee_sample(logits.data_ptr(), _rows(logits, "logits"), m, v, _ptr(temperature), _ptr(uniform),
                            out.data_ptr(), _ptr(slots), _ptr(feedback), _stream()), lib)
+
+
+CHAIN_MAX_K = 64            # largest top-k the device chain takes
+CHAIN_HISTORY = 256         # tokens of recent history kept per request slot for the repeat penalty
+CHAIN_CHUNK = 2048
+
+
+def chain_scratch_floats(rows: int, vocab: int) -> int:
+    return rows * -(-vocab // CHAIN_CHUNK) * CHAIN_MAX_K * 2
+
+
+def sample_chain(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
+                 slots: Optional[torch.Tensor] = None, feedback: Optional[torch.Tensor] = None,
+                 history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
+                 penalise: bool = False) -> None:
+    """The reference's sampling chain on the device: repeat penalty over the request's recent tokens
+    (``history`` [slots, cap] rings with ``history_len`` [slots] tokens appended so far), the top-k
+    logits (1 <= k <= CHAIN_MAX_K; greedy rows are k = 1), float64 probabilities, top-p and min-p
+    cuts, the draw.  ``params`` [m, 8] float64 per row: temperature, top_k, top_p, min_p, repeat
+    penalty, repeat_last_n, uniform number, unused.  ``logits`` is changed in place where a row
+    penalises; the choice is appended to the request's ring and stored in ``feedback[slots[r]]``."""
+    lib = library()
+    m, v = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.is_contiguous()
+    assert params.dtype == torch.float64 and params.is_contiguous() and tuple(params.shape) == (m, 8)
+    assert scratch.dtype == torch.float32 and scratch.numel() >= chain_scratch_floats(m, v)
+    _i32(slots, "slots"); _i32(feedback, "feedback"); _i32(history, "history"); _i32(history_len, "history_len")
+    cap = history.shape[1] if history is not None else 0
+    _check(lib.hfee_sample_chain(logits.data_ptr(), _rows(logits, "logits"), m, v, params.data_ptr(), _ptr(slots),
+                                 _ptr(history), cap, _ptr(history_len), int(penalise), scratch.data_ptr(),
+                                 scratch.numel(), out.data_ptr(), _ptr(feedback), _stream()), lib)
+    count_launches(2 if penalise else 1)
 
 
 ARGMAX_CHUNKS = 64

@@ -39,3 +39,13 @@ class SamplingOptions:
         if self.temperature <= 0:
             return True
         return self.top_k <= 0 and not (0 < self.top_p < 1) and not self.min_p > 0
+
+    @property
+    def device_chain(self) -> bool:
+        """True when the device kernels for the whole chain take these options: a top-k of at most
+        64 (greedy is k = 1) and a repeat penalty over at most the last 256 tokens."""
+        if self.penalises and not 0 < self.repeat_last_n <= 256:
+            return False
+        if self.temperature <= 0:
+            return True
+        return 0 < self.top_k <= 64

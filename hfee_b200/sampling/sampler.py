@@ -7,8 +7,11 @@ cuts, and a draw ``r = U * total`` that walks the kept candidates.  The uniform
 number U comes from a counter-based generator keyed by (seed, draw index), so a
 request's draws do not depend on what else is in the batch or on preemption.
 
-Greedy and plain temperature sampling run in a device kernel over the whole batch;
-options that truncate or penalise take the same logits through the host chain.
+Greedy and plain temperature sampling run in a device kernel over the whole batch.  The
+whole chain runs on the device too when every row's top-k is at most 64 and its penalty looks
+at no more than 256 recent tokens (the reference's defaults are 40 and 64): the recent tokens
+of each request are kept in a ring on the device, so generation stays pipelined.  Other options
+take the same logits through the host chain.
 """
 from __future__ import annotations
 
@@ -67,9 +70,12 @@ def sample_host(logits: np.ndarray, history: Sequence[int], opts: SamplingOption
     if opts.temperature <= 0:
         return int(np.argmax(logits))               # first maximum, sampler.go:77-83
     k = opts.top_k if 0 < opts.top_k <= logits.shape[0] else logits.shape[0]
+    # descending logits, equal logits by ascending id (the reference's sort leaves ties in no
+    # particular order; the device kernels use this one)
     if k < logits.shape[0]:
-        idx = np.argpartition(-logits, k - 1)[:k]
-        idx = idx[np.argsort(-logits[idx], kind="stable")]
+        kth = np.partition(logits, logits.shape[0] - k)[logits.shape[0] - k]      # the k-th largest value
+        idx = np.nonzero(logits >= kth)[0]
+        idx = idx[np.argsort(-logits[idx], kind="stable")][:k]
     else:
         idx = np.argsort(-logits, kind="stable")
     cand = logits[idx]
@@ -110,6 +116,37 @@ class BatchSampler:
         self.out_hosts = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self.turn = 0
         self.argmax_scratch = torch.zeros(max_rows * ops.ARGMAX_CHUNKS * 2, dtype=torch.float32, device=self.device)
+        # the device chain: per-row parameters (two pinned copies used in turn), candidates, history rings
+        self.params = torch.zeros(max_rows, 8, dtype=torch.float64, device=self.device)
+        self.params_host = [torch.zeros(max_rows, 8, dtype=torch.float64, pin_memory=pin) for _ in range(2)]
+        self.chain_scratch: Optional[torch.Tensor] = None
+        self.use_device_chain = True          # False: truncating or penalising options always go through the host chain
+        self.history = torch.zeros(max_rows, ops.CHAIN_HISTORY, dtype=torch.int32, device=self.device)
+        self.history_len = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        # the same for the unpipelined path, where the host rewrites the rings before every draw
+        self.row_history = torch.zeros(max_rows, ops.CHAIN_HISTORY, dtype=torch.int32, device=self.device)
+        self.row_history_len = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.rows = torch.arange(max_rows, dtype=torch.int32, device=self.device)
+
+    @staticmethod
+    def _chain_params(o: SamplingOptions, u: float) -> List[float]:
+        """A row of parameters for the device chain; top-p, min-p and the penalty rounded to float32 as
+        the reference holds them."""
+        return [max(o.temperature, 0.0), o.top_k, float(np.float32(o.top_p)), float(np.float32(o.min_p)),
+                float(np.float32(o.repeat_penalty)) if o.penalises else 1.0, o.repeat_last_n if o.penalises else 0, u, 0.0]
+
+    def _chain_scratch(self, vocab: int) -> torch.Tensor:
+        need = ops.chain_scratch_floats(self.max_rows, vocab)
+        if self.chain_scratch is None or self.chain_scratch.numel() < need:
+            self.chain_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+        return self.chain_scratch
+
+    def load_history(self, slot: int, tokens: Sequence[int]) -> None:
+        """Start the ring of recent tokens of the request in ``slot`` from its tokens so far."""
+        tail = [int(t) for t in tokens[-ops.CHAIN_HISTORY:]]
+        if tail:
+            self.history[slot, :len(tail)].copy_(torch.tensor(tail, dtype=torch.int32))
+        self.history_len[slot:slot + 1].fill_(len(tail))
 
     def sample(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
                draws: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
@@ -118,6 +155,23 @@ class BatchSampler:
         m = logits.shape[0]
         assert m == len(options) <= self.max_rows
         us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
+        if (self.use_device_chain and self.device.type == "cuda" and not all(o.device_only for o in options)
+                and all(o.device_chain for o in options)):
+            # the whole chain on the device; the host knows every row's history here, so the rings of
+            # recent tokens are simply written anew (rows stand in for request slots)
+            cap = ops.CHAIN_HISTORY
+            tails = [[int(t) for t in h[-cap:]] if o.penalises else [] for h, o in zip(histories, options)]
+            ring = torch.zeros(m, cap, dtype=torch.int32)
+            for i, t in enumerate(tails):
+                if t:
+                    ring[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+            self.row_history[:m].copy_(ring)
+            self.row_history_len[:m].copy_(torch.tensor([len(t) for t in tails], dtype=torch.int32))
+            self.params[:m].copy_(torch.tensor([self._chain_params(o, u) for o, u in zip(options, us)], dtype=torch.float64))
+            ops.sample_chain(logits, self.params[:m], self.out[:m], self._chain_scratch(logits.shape[1]), self.rows[:m], None,
+                             self.row_history, self.row_history_len, penalise=any(o.penalises for o in options))
+            self.out_host[:m].copy_(self.out[:m])
+            return [int(t) for t in self.out_host[:m]]
         if all(o.temperature <= 0 for o in options) and all(o.device_only for o in options):
             ops.argmax(logits, self.out[:m], self.argmax_scratch)
         else:
@@ -136,15 +190,25 @@ class BatchSampler:
     # -- pipelined use: launch now, read the result one step later -------------------------------
     def launch(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
                draws: Sequence[int], slots: torch.Tensor, feedback: torch.Tensor):
-        """Start choosing a token for each row on the device (options must all be ``device_only``):
-        the choices go to ``feedback[slots[r]]`` for the next step and, asynchronously, to pinned
+        """Start choosing a token for each row on the device (options must all be ``device_only``
+        or all ``device_chain``): the choices go to ``feedback[slots[r]]`` for the next step and, asynchronously, to pinned
         host memory.  Returns a handle for :meth:`fetch`."""
         m = logits.shape[0]
-        assert m == len(options) <= self.max_rows and all(o.device_only for o in options)
+        assert m == len(options) <= self.max_rows
+        simple = all(o.device_only for o in options)
+        assert simple or all(o.device_chain for o in options)
         b = self.turn
         self.turn ^= 1
         out = self.outs[b][:m]
-        if all(o.temperature <= 0 for o in options):
+        if not simple:
+            host = self.params_host[b]
+            for i, o in enumerate(options):
+                u = uniform(seeds[i], 0, draws[i]) if o.temperature > 0 else 0.0
+                host[i] = torch.tensor(self._chain_params(o, u), dtype=torch.float64)
+            self.params[:m].copy_(host[:m], non_blocking=True)
+            ops.sample_chain(logits, self.params[:m], out, self._chain_scratch(logits.shape[1]), slots, feedback, self.history,
+                             self.history_len, penalise=any(o.penalises for o in options))
+        elif all(o.temperature <= 0 for o in options):
             ops.argmax(logits, out, self.argmax_scratch, slots, feedback)
         else:
             us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
