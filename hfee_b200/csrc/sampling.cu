@@ -1,7 +1,8 @@
 // Next-token choice on the device over float32 logits [M, V]: argmax where a
 // row's temperature is <= 0 (first maximum wins), else one draw from
-// softmax(logits / T) by inverse CDF in index order with the uniform number the
-// host supplies for that row.
+// softmax(logits / T) by inverse CDF with the uniform number the host supplies
+// for that row, walking the tokens in one fixed order (chunks of 2,048 ids; in a
+// chunk the ids t, t + 256, ... of thread t = 0..255 in turn).
 // Reference: hostfog/hfee internal/llm/sampler.go:76-84 (greedy, strict '>'),
 // :88-95 (probabilities relative to the maximum, float64), :118-129 (draw).
 #include "common.cuh"
@@ -9,80 +10,6 @@
 namespace {
 
 constexpr int THREADS = 256;
-
-__global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
-              const double* __restrict__ uniform, int* __restrict__ out, const int* __restrict__ slots,
-              int* __restrict__ feedback) {
-  pdl_wait();
-  pdl_launch_dependents();
-  __shared__ float s_val[THREADS];
-  __shared__ int s_idx[THREADS];
-  __shared__ double s_sum[THREADS];
-  int r = blockIdx.x, tid = threadIdx.x;
-  const float* row = logits + (long long)r * ld;
-
-  // contiguous chunk per thread so that index order is kept
-  int chunk = (V + THREADS - 1) / THREADS;
-  int begin = min(V, tid * chunk), end = min(V, begin + chunk);
-
-  float best = -INFINITY;
-  int best_i = V;          // V = "none"
-  for (int c = begin; c < end; ++c) {
-    float v = row[c];
-    if (best_i == V || v > best) { best = v; best_i = c; }
-  }
-  s_val[tid] = best;
-  s_idx[tid] = best_i;
-  __syncthreads();
-  for (int o = THREADS / 2; o > 0; o >>= 1) {
-    if (tid < o) {
-      float v2 = s_val[tid + o];
-      int i2 = s_idx[tid + o];
-      // keep the lower index on ties; an empty chunk (index V) never wins
-      if (i2 < V && (s_idx[tid] == V || v2 > s_val[tid] || (v2 == s_val[tid] && i2 < s_idx[tid]))) {
-        s_val[tid] = v2;
-        s_idx[tid] = i2;
-      }
-    }
-    __syncthreads();
-  }
-  float vmax = s_val[0];
-  int imax = s_idx[0];
-  float T = temperature ? temperature[r] : 0.f;
-  if (!(T > 0.f)) {
-    if (tid == 0) {
-      out[r] = imax;
-      if (feedback) feedback[slots[r]] = imax;
-    }
-    return;
-  }
-
-  double local = 0.0;
-  for (int c = begin; c < end; ++c) local += exp((double)((row[c] - vmax) / T));
-  s_sum[tid] = local;
-  __syncthreads();
-  if (tid == 0) {
-    double total = 0.0;
-    for (int t = 0; t < THREADS; ++t) total += s_sum[t];
-    double target = uniform[r] * total;
-    // find the chunk, then the element, where the running sum first reaches the target
-    int t = 0;
-    double run = 0.0;
-    while (t < THREADS - 1 && run + s_sum[t] < target) run += s_sum[t++];
-    int b = min(V, t * chunk), e = min(V, b + chunk);
-    int pick = imax;
-    bool found = false;
-    for (int c = b; c < e; ++c) {
-      run += exp((double)((row[c] - vmax) / T));
-      pick = c;
-      if (run >= target) { found = true; break; }
-    }
-    if (!found && e == b) pick = imax;
-    out[r] = pick;
-    if (feedback) feedback[slots[r]] = pick;
-  }
-}
 
 // Greedy choice for many rows at once: each row's columns are divided among `chunks` blocks
 // (stage 1), then one block per row picks among the chunk winners (stage 2).  Ties go to the
@@ -164,6 +91,169 @@ argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __r
 }
 
 
+// One round of "largest remaining value, lowest index on ties" over a block: every thread offers its
+// best, the winner is broadcast.  An offer with index `none` never wins.
+__device__ __forceinline__ void block_best(float& val, int& idx, int none, float* s_val, int* s_idx) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, val, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
+  }
+  __syncthreads();                                             // the previous round's winner has been read
+  if (lane == 0) { s_val[warp] = val; s_idx[warp] = idx; }
+  __syncthreads();
+  val = s_val[0]; idx = s_idx[0];
+#pragma unroll
+  for (int w = 1; w < THREADS / 32; ++w) {
+    const float v2 = s_val[w];
+    const int i2 = s_idx[w];
+    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Plain temperature sampling over all tokens in two stages.  Stage 1, one block per (row, chunk of
+// 2,048 ids): the chunk's maximum with its first position, and the sum of exp((x - max) / T) in
+// float64.  Stage 2, one block per row: the row maximum (greedy rows end here), the chunks' sums
+// brought to that maximum, the chunk in which the running sum reaches U * total, then the thread and
+// the element inside that chunk.  All sums are taken in fixed orders, so a row's draw does not depend
+// on the batch.
+struct ChunkStat { float max; int first; double sum; };
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS)
+temperature_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int chunks,
+                          const float* __restrict__ temperature, ChunkStat* __restrict__ stats) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float s_val[THREADS / 32];
+  __shared__ int s_idx[THREADS / 32];
+  __shared__ double s_sum[THREADS / 32];
+  constexpr int NE = 2048 / THREADS;
+  const int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
+  const float T = temperature ? temperature[r] : 0.f;
+  const float* row = logits + (long long)r * ld;
+  const int begin = ch * 2048;
+  float v[NE];
+  float bv = 0.f;
+  int bi = V;
+#pragma unroll
+  for (int j = 0; j < NE; ++j) {
+    const int c = begin + tid + j * THREADS;
+    v[j] = c < V ? row[c] : 0.f;
+    if (c < V && (bi == V || v[j] > bv)) { bv = v[j]; bi = c; }       // ascending ids: the first maximum stays
+  }
+  float m = bv;
+  int first = bi;
+  block_best(m, first, V, s_val, s_idx);
+  double sum = 0.0;
+  if (T > 0.f) {
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+      if (begin + tid + j * THREADS < V) sum += exp((double)((v[j] - m) / T));
+    sum = warp_sum_f64(sum);
+    if ((tid & 31) == 0) s_sum[tid >> 5] = sum;
+    __syncthreads();
+    sum = 0.0;
+    for (int w = 0; w < THREADS / 32; ++w) sum += s_sum[w];
+  }
+  if (tid == 0) stats[(long long)r * chunks + ch] = ChunkStat{m, first, sum};
+}
+
+__global__ void __launch_bounds__(THREADS)
+temperature_stage2_kernel(const float* __restrict__ logits, long long ld, int V, int chunks,
+                          const float* __restrict__ temperature, const double* __restrict__ uniform,
+                          const ChunkStat* __restrict__ stats, int* __restrict__ out, const int* __restrict__ slots,
+                          int* __restrict__ feedback) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ double part[THREADS];
+  __shared__ int s_chunk, s_thread, s_greedy;
+  __shared__ float s_max;
+  __shared__ double s_left;
+  constexpr int NE = 2048 / THREADS;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float T = temperature ? temperature[r] : 0.f;
+  const ChunkStat* st = stats + (long long)r * chunks;
+  if (tid == 0) {
+    float M = st[0].max;
+    int imax = st[0].first;
+    for (int c = 1; c < chunks; ++c)
+      if (st[c].first < V && (imax == V || st[c].max > M)) { M = st[c].max; imax = st[c].first; }      // chunks ascend: the first maximum stays
+    s_greedy = imax;
+    s_chunk = -1;
+    if (T > 0.f) {
+      double total = 0.0;
+      for (int c = 0; c < chunks; ++c) total += st[c].sum * exp((double)((st[c].max - M) / T));
+      const double target = uniform[r] * total;
+      double run = 0.0;
+      int pick = 0;
+      double before = 0.0;
+      for (int c = 0; c < chunks; ++c) {
+        const double w = st[c].sum * exp((double)((st[c].max - M) / T));
+        if (w > 0.0) { pick = c; before = run; }
+        if (run + w >= target) break;
+        run += w;
+      }
+      s_chunk = pick;
+      s_max = st[pick].max;
+      s_left = (target - before) / exp((double)((st[pick].max - M) / T));       // in the chunk's own scale
+    }
+  }
+  __syncthreads();
+  if (s_chunk < 0) {
+    if (tid == 0) {
+      out[r] = s_greedy;
+      if (feedback) feedback[slots[r]] = s_greedy;
+    }
+    return;
+  }
+  const float* row = logits + (long long)r * ld;
+  const int begin = s_chunk * 2048;
+  double e[NE];
+  double mine = 0.0;
+#pragma unroll
+  for (int j = 0; j < NE; ++j) {
+    const int c = begin + tid + j * THREADS;
+    e[j] = c < V ? exp((double)((row[c] - s_max) / T)) : 0.0;
+    mine += e[j];
+  }
+  part[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    double run = 0.0, before = 0.0;
+    int pick = 0;
+    for (int t = 0; t < THREADS; ++t) {
+      if (part[t] > 0.0) { pick = t; before = run; }
+      if (run + part[t] >= s_left) break;
+      run += part[t];
+    }
+    s_thread = pick;
+    s_left -= before;
+  }
+  __syncthreads();
+  if (tid != s_thread) return;
+  double run = 0.0;
+  int token = s_greedy;
+#pragma unroll
+  for (int j = 0; j < NE; ++j) {
+    const int c = begin + tid + j * THREADS;
+    if (c >= V) break;
+    run += e[j];
+    token = c;
+    if (run >= s_left) break;
+  }
+  out[r] = token;
+  if (feedback) feedback[slots[r]] = token;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The whole chain of hostfog/hfee internal/llm/sampler.go:54-130 on the device, for rows whose
 // top-k is between 1 and CHAIN_MAX_K (a greedy row is the chain with k = 1): repeat penalty over the
@@ -202,28 +292,6 @@ chain_penalty_kernel(float* __restrict__ logits, long long ld, int V, const doub
   if (tok < 0 || tok >= V) return;
   float* x = logits + (long long)r * ld + tok;
   *x = *x > 0.f ? *x / pen : *x * pen;
-}
-
-// One round of "largest remaining value, lowest index on ties" over a block: every thread offers its
-// best, the winner is broadcast.  An offer with index `none` never wins.
-__device__ __forceinline__ void block_best(float& val, int& idx, int none, float* s_val, int* s_idx) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float v2 = __shfl_xor_sync(0xffffffffu, val, o);
-    const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
-  }
-  __syncthreads();                                             // the previous round's winner has been read
-  if (lane == 0) { s_val[warp] = val; s_idx[warp] = idx; }
-  __syncthreads();
-  val = s_val[0]; idx = s_idx[0];
-#pragma unroll
-  for (int w = 1; w < THREADS / 32; ++w) {
-    const float v2 = s_val[w];
-    const int i2 = s_idx[w];
-    if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
-  }
 }
 
 // Stage 1: the k largest of each chunk of a row, in descending order, to cand[(row, chunk)][CHAIN_MAX_K] as
@@ -367,12 +435,20 @@ HFEE_API int hfee_argmax(const float* logits, long long ld, int M, int V, int ch
   return hfee_check_launch("argmax");
 }
 
+// scratch: M * ceil(V / 2048) * 2 doubles (16-byte aligned).
 HFEE_API int hfee_sample(const float* logits, long long ld, int M, int V, const float* temperature,
-                         const double* uniform, int* out, const int* slots, int* feedback, cudaStream_t stream) {
+                         const double* uniform, double* scratch, long long scratch_doubles, int* out, const int* slots,
+                         int* feedback, cudaStream_t stream) {
   if (M == 0) return HFEE_OK;
-  HFEE_REQUIRE(M > 0 && V > 0 && ld >= V, "sample: bad sizes M=%d V=%d ld=%lld", M, V, ld);
+  HFEE_REQUIRE(M > 0 && M <= 65535 && V > 0 && ld >= V, "sample: bad sizes M=%d V=%d ld=%lld", M, V, ld);
   HFEE_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures need uniform numbers");
-  hfee_launch(sample_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, temperature, uniform, out, slots, feedback);
+  const int chunks = (V + 2047) / 2048;
+  HFEE_REQUIRE(scratch != nullptr && scratch_doubles >= (long long)M * chunks * 2 && (uintptr_t)scratch % 16 == 0,
+               "sample: the scratch must hold %lld doubles", (long long)M * chunks * 2);
+  hfee_launch(temperature_stage1_kernel, dim3((unsigned)chunks, (unsigned)M), dim3(THREADS), 0, stream, logits, ld, V, chunks,
+              temperature, (ChunkStat*)scratch);
+  hfee_launch(temperature_stage2_kernel, dim3(M), dim3(THREADS), 0, stream, logits, ld, V, chunks, temperature, uniform,
+              (const ChunkStat*)scratch, out, slots, feedback);
   return hfee_check_launch("sample");
 }
 

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "hfee_attention_mma_rope": [_P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P],
     "hfee_sample_chain": [_P, _L, _I, _I, _P, _P, _P, _I, _P, _I, _P, _L, _P, _P, _P],
 }
@@ -579,8 +579,10 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
            uniform: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
            feedback: Optional[torch.Tensor] = None) -> None:
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or no temperatures are given),
-    else a draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1).  With ``slots``
-    and ``feedback`` the choice is also stored in ``feedback[slots[r]]``."""
+    else a draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1): the inverse CDF
+    over the tokens in the fixed order of the kernel (chunks of 2,048 ids; in a chunk the ids
+    t, t + 256, ... of t = 0..255 in turn).  With ``slots`` and ``feedback`` the choice is also stored
+    in ``feedback[slots[r]]``."""
     lib = library()
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.is_contiguous()
     _i32(slots, "slots"); _i32(feedback, "feedback")
@@ -588,8 +590,17 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     m, v = logits.shape
     if temperature is not None:
         assert temperature.dtype == torch.float32 and uniform.dtype == torch.float64
+    global _SAMPLE_SCRATCH
+    need = m * -(-v // CHAIN_CHUNK) * 2
+    if _SAMPLE_SCRATCH is None or _SAMPLE_SCRATCH.numel() < need:
+        _SAMPLE_SCRATCH = torch.empty(max(need, 64 * 64 * 2), dtype=torch.float64, device=logits.device)
     _check(lib.hfee_sample(logits.data_ptr(), _rows(logits, "logits"), m, v, _ptr(temperature), _ptr(uniform),
-                           out.data_ptr(), _ptr(slots), _ptr(feedback), _stream()), lib)
+                           _SAMPLE_SCRATCH.data_ptr(), _SAMPLE_SCRATCH.numel(), out.data_ptr(), _ptr(slots),
+                           _ptr(feedback), _stream()), lib)
+    count_launches(1)
+
+
+_SAMPLE_SCRATCH: Optional[torch.Tensor] = None
 
 
 CHAIN_MAX_K = 64            # largest top-k the device chain takes

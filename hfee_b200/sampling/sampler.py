@@ -119,6 +119,8 @@ class BatchSampler:
         # the device chain: per-row parameters (two pinned copies used in turn), candidates, history rings
         self.params = torch.zeros(max_rows, 8, dtype=torch.float64, device=self.device)
         self.params_host = [torch.zeros(max_rows, 8, dtype=torch.float64, pin_memory=pin) for _ in range(2)]
+        self.temp_host = [torch.zeros(max_rows, dtype=torch.float32, pin_memory=pin) for _ in range(2)]
+        self.unif_host = [torch.zeros(max_rows, dtype=torch.float64, pin_memory=pin) for _ in range(2)]
         self.chain_scratch: Optional[torch.Tensor] = None
         self.use_device_chain = True          # False: truncating or penalising options always go through the host chain
         self.history = torch.zeros(max_rows, ops.CHAIN_HISTORY, dtype=torch.int32, device=self.device)
@@ -212,8 +214,10 @@ class BatchSampler:
             ops.argmax(logits, out, self.argmax_scratch, slots, feedback)
         else:
             us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
-            self.temp[:m].copy_(torch.tensor([o.temperature for o in options], dtype=torch.float32))
-            self.unif[:m].copy_(torch.tensor(us, dtype=torch.float64))
+            self.temp_host[b][:m] = torch.tensor([o.temperature for o in options], dtype=torch.float32)
+            self.unif_host[b][:m] = torch.tensor(us, dtype=torch.float64)
+            self.temp[:m].copy_(self.temp_host[b][:m], non_blocking=True)        # pinned: the host does not wait
+            self.unif[:m].copy_(self.unif_host[b][:m], non_blocking=True)
             ops.sample(logits, out, self.temp[:m], self.unif[:m], slots, feedback)
         self.out_hosts[b][:m].copy_(out, non_blocking=True)
         event = torch.cuda.Event() if self.device.type == "cuda" else None

@@ -215,13 +215,18 @@ def test_sample_greedy_and_temperature(ops, m, v):
     for u in (0.0, 0.25, 0.5, 0.999999):
         un = torch.full((m,), u, dtype=torch.float64, device=DEV)
         ops.sample(logits, out, temp, un)
+        # the kernel's fixed order: chunks of 2,048 ids; in a chunk the ids t, t + 256, ... for t = 0..255
+        order = torch.tensor([c for b in range(0, v, 2048) for t in range(256) for c in range(b + t, min(b + 2048, v), 256)])
+        assert sorted(order.tolist()) == list(range(v))
         for i in range(m):
-            p = torch.exp((logits[i].double().cpu() - logits[i].double().max().cpu()) / 0.7)
+            p = torch.exp((logits[i].double().cpu() - logits[i].double().max().cpu()) / 0.7)[order]
             cum = torch.cumsum(p, 0)
-            want = int(torch.searchsorted(cum, u * float(cum[-1])).clamp(max=v - 1))
+            at = int(torch.searchsorted(cum, u * float(cum[-1])).clamp(max=v - 1))
+            want = int(order[at])
             got = int(out[i])
+            where = int((order == got).nonzero()[0])
             # equal up to rounding of the running sum at the boundary
-            assert got == want or abs(float(cum[got] - cum[want])) / float(cum[-1]) < 1e-9
+            assert got == want or abs(float(cum[where] - cum[at])) / float(cum[-1]) < 1e-9
 
 
 @pytest.mark.parametrize("m", [1, 8, 17, 64])
