@@ -92,23 +92,26 @@ argmax_stage2_kernel(const float* __restrict__ part, int V, int chunks, int* __r
 
 
 // One round of "largest remaining value, lowest index on ties" over a block: every thread offers its
-// best, the winner is broadcast.  An offer with index `none` never wins.
-__device__ __forceinline__ void block_best(float& val, int& idx, int none, float* s_val, int* s_idx) {
+// best, the winner is broadcast.  An offer with index `none` never wins.  `s_val`/`s_idx` hold two
+// sets of per-warp slots used in turn (`round` & 1), so one barrier per round is enough.
+__device__ __forceinline__ void block_best(float& val, int& idx, int none, float* s_val, int* s_idx, int round = 0) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int WARPS = THREADS / 32;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float v2 = __shfl_xor_sync(0xffffffffu, val, o);
     const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
     if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
   }
-  __syncthreads();                                             // the previous round's winner has been read
-  if (lane == 0) { s_val[warp] = val; s_idx[warp] = idx; }
+  float* sv = s_val + (round & 1) * WARPS;
+  int* si = s_idx + (round & 1) * WARPS;
+  if (lane == 0) { sv[warp] = val; si[warp] = idx; }
   __syncthreads();
-  val = s_val[0]; idx = s_idx[0];
+  val = sv[0]; idx = si[0];
 #pragma unroll
-  for (int w = 1; w < THREADS / 32; ++w) {
-    const float v2 = s_val[w];
-    const int i2 = s_idx[w];
+  for (int w = 1; w < WARPS; ++w) {
+    const float v2 = sv[w];
+    const int i2 = si[w];
     if (i2 != none && (idx == none || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
   }
 }
@@ -133,8 +136,8 @@ temperature_stage1_kernel(const float* __restrict__ logits, long long ld, int V,
                           const float* __restrict__ temperature, ChunkStat* __restrict__ stats) {
   pdl_wait();
   pdl_launch_dependents();
-  __shared__ float s_val[THREADS / 32];
-  __shared__ int s_idx[THREADS / 32];
+  __shared__ float s_val[2 * THREADS / 32];
+  __shared__ int s_idx[2 * THREADS / 32];
   __shared__ double s_sum[THREADS / 32];
   constexpr int NE = 2048 / THREADS;
   const int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
@@ -301,8 +304,8 @@ chain_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int c
                     float2* __restrict__ cand) {
   pdl_wait();
   pdl_launch_dependents();
-  __shared__ float s_val[THREADS / 32];
-  __shared__ int s_idx[THREADS / 32];
+  __shared__ float s_val[2 * THREADS / 32];
+  __shared__ int s_idx[2 * THREADS / 32];
   constexpr int NE = CHAIN_CHUNK / THREADS;
   const int r = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
   const double temp = params[r * CHAIN_PARAMS];
@@ -327,84 +330,109 @@ chain_stage1_kernel(const float* __restrict__ logits, long long ld, int V, int c
     float val = bv;
     int idx = bj >= 0 ? begin + tid + bj * THREADS : V;
     const int mine = idx;
-    block_best(val, idx, V, s_val, s_idx);
+    block_best(val, idx, V, s_val, s_idx, round);
     if (idx != V && idx == mine) alive &= ~(1u << bj);
     if (tid == 0) dst[round] = make_float2(val, __int_as_float(idx));
   }
 }
 
-// Stage 2: the k largest of a row's candidates, then the chain.  Appends the choice to the request's
-// history ring (when there is one) and stores it in feedback[slot] for the next step's embedding.
+// Stage 2: the k largest of a row's candidates, then the chain.  The chunks' lists are sorted, so the
+// next largest is always at the head of some list: one warp merges them (lane l owns the lists l,
+// l + 32, ...; a round is a comparison of the lanes' best heads by shuffles, no barrier).  Appends
+// the choice to the request's history ring (when there is one) and stores it in feedback[slot] for
+// the next step's embedding.
 __global__ void __launch_bounds__(THREADS)
 chain_stage2_kernel(const float2* __restrict__ cand, int V, int chunks, const double* __restrict__ params,
                     const int* __restrict__ slots, int* __restrict__ history, int cap, int* __restrict__ history_len,
                     int* __restrict__ out, int* __restrict__ feedback) {
   pdl_wait();
   pdl_launch_dependents();
-  __shared__ float s_val[THREADS / 32];
-  __shared__ int s_idx[THREADS / 32];
+  extern __shared__ float2 lists[];                             // [chunks][k]
   __shared__ float top_val[CHAIN_MAX_K];
   __shared__ int top_idx[CHAIN_MAX_K];
   __shared__ double prob[CHAIN_MAX_K];
-  constexpr int NE = 32;                                        // up to 128 chunks x 64 candidates over 256 threads
+  __shared__ double s_sum;
+  __shared__ int s_n;
   const int r = blockIdx.x, tid = threadIdx.x;
   const double* pr = params + r * CHAIN_PARAMS;
   const double temp = pr[0];
   const int k = temp > 0.0 ? min(max((int)pr[1], 1), CHAIN_MAX_K) : 1;
-  const int total = chunks * k;                                 // candidate e = chunk e / k, place e % k
-  float v[NE];
-  int id[NE];
+  for (int e = tid; e < chunks * k; e += THREADS)
+    lists[e] = cand[((long long)r * chunks + e / k) * CHAIN_MAX_K + e % k];
+  __syncthreads();
+  if (tid < 32) {
+    constexpr int OWN = 4;                                      // up to 128 chunks over 32 lanes
+    int pos[OWN];
 #pragma unroll
-  for (int j = 0; j < NE; ++j) {
-    const int e = tid + j * THREADS;
-    id[j] = V;
-    v[j] = 0.f;
-    if (e < total) {
-      const float2 c = cand[((long long)r * chunks + e / k) * CHAIN_MAX_K + e % k];
-      v[j] = c.x;
-      id[j] = __float_as_int(c.y);
+    for (int j = 0; j < OWN; ++j) pos[j] = 0;
+    for (int round = 0; round < k; ++round) {
+      float bv = 0.f;
+      int bi = V, bj = 0;
+#pragma unroll
+      for (int j = 0; j < OWN; ++j) {
+        const int c = tid + j * 32;
+        if (c < chunks && pos[j] < k) {
+          const float2 h = lists[c * k + pos[j]];
+          const int hi = __float_as_int(h.y);
+          if (hi != V && (bi == V || h.x > bv || (h.x == bv && hi < bi))) { bv = h.x; bi = hi; bj = j; }
+        }
+      }
+      float val = bv;
+      int idx = bi;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, val, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (i2 != V && (idx == V || v2 > val || (v2 == val && i2 < idx))) { val = v2; idx = i2; }
+      }
+      if (idx != V && idx == bi) {
+#pragma unroll
+        for (int j = 0; j < OWN; ++j)
+          if (j == bj) ++pos[j];
+      }
+      if (tid == 0) { top_val[round] = val; top_idx[round] = idx; }
     }
-  }
-  for (int round = 0; round < k; ++round) {
-    float bv = 0.f;
-    int bi = V, bj = -1;
-#pragma unroll
-    for (int j = 0; j < NE; ++j)
-      if (id[j] != V && (bi == V || v[j] > bv || (v[j] == bv && id[j] < bi))) { bv = v[j]; bi = id[j]; bj = j; }
-    float val = bv;
-    int idx = bi;
-    block_best(val, idx, V, s_val, s_idx);
-    if (idx != V && idx == bi) id[bj] = V;
-    if (tid == 0) { top_val[round] = val; top_idx[round] = idx; }
   }
   __syncthreads();
   if (temp > 0.0 && tid < k)
     prob[tid] = top_idx[tid] != V ? exp((double)((top_val[tid] - top_val[0]) / (float)temp)) : 0.0;
   __syncthreads();
-  if (tid != 0) return;
-  int token = top_idx[0];
-  if (temp > 0.0) {
+  // probabilities p_i = prob_i / sum: the sum by one thread in candidate order, the divisions (slow in
+  // float64) by the candidates' threads, so that the walk below only adds and compares
+  if (tid == 0) {
     int n = 0;
     double sum = 0.0;
     while (n < k && top_idx[n] != V) sum += prob[n++];
+    s_sum = sum;
+    s_n = n;
+  }
+  __syncthreads();
+  if (temp > 0.0 && tid < k) prob[tid] = prob[tid] / s_sum;
+  __syncthreads();
+  if (tid != 0) return;
+  int token = top_idx[0];
+  if (temp > 0.0) {
+    const int n = s_n;
     const double top_p = pr[2], min_p = pr[3];
     int keep = n;
     if (top_p > 0.0 && top_p < 1.0) {
       double cum = 0.0;
       for (int i = 0; i < n; ++i) {
-        cum += prob[i] / sum;
+        cum += prob[i];
         if (cum >= top_p) { keep = i + 1; break; }
       }
     }
-    if (min_p > 0.0)
+    if (min_p > 0.0) {
+      const double floor_p = min_p * prob[0];
       for (int i = 1; i < keep; ++i)
-        if (prob[i] / sum < min_p * (prob[0] / sum)) { keep = i; break; }
+        if (prob[i] < floor_p) { keep = i; break; }
+    }
     double kept = 0.0;
-    for (int i = 0; i < keep; ++i) kept += prob[i] / sum;
+    for (int i = 0; i < keep; ++i) kept += prob[i];
     double left = pr[6] * kept;
     token = top_idx[keep - 1];
     for (int i = 0; i < keep; ++i) {
-      left -= prob[i] / sum;
+      left -= prob[i];
       if (left <= 0.0) { token = top_idx[i]; break; }
     }
   }
@@ -474,7 +502,15 @@ HFEE_API int hfee_sample_chain(float* logits, long long ld, int M, int V, const 
                 history_cap, (const int*)history_len);
   hfee_launch(chain_stage1_kernel, dim3((unsigned)chunks, (unsigned)M), dim3(THREADS), 0, stream, (const float*)logits, ld, V,
               chunks, params, (float2*)scratch);
-  hfee_launch(chain_stage2_kernel, dim3(M), dim3(THREADS), 0, stream, (const float2*)scratch, V, chunks, params, slots, history,
-              history_cap, history_len, out, feedback);
+  // the candidate lists of a row in shared memory: chunks * CHAIN_MAX_K pairs at most (64 KB at 128 chunks)
+  const size_t list_bytes = (size_t)chunks * CHAIN_MAX_K * sizeof(float2);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(chain_stage2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * CHAIN_MAX_K * (int)sizeof(float2));
+    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "sample_chain: cannot get shared memory for the candidate lists: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  hfee_launch(chain_stage2_kernel, dim3(M), dim3(THREADS), list_bytes, stream, (const float2*)scratch, V, chunks, params, slots,
+              history, history_cap, history_len, out, feedback);
   return hfee_check_launch("sample_chain");
 }
