@@ -172,7 +172,7 @@ def test_gemm_stream(ops, m, n, k):
     _close(acc, base.double() + ref, 1e-5)
 
 
-@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("m", [1, 8, 9, 16, 20, 64])
 @pytest.mark.parametrize("inner,k", [(4, 8), (172, 64), (1000, 96), (8192, 256), (10004, 4104)])
 def test_gemm_stream_swiglu(ops, m, inner, k):
     g = torch.Generator().manual_seed(7)
