@@ -192,13 +192,29 @@ attention_mma_kernel(AttnParams p) {
     __nv_bfloat16* vd = v_s + stage * BLOCK_N * PITCH;
     long long off[PIECES];
     bool ok[PIECES];
+    if (p.cache.page_size >= BLOCK_N) {
+      // a block lies inside one page (both are powers of two, blocks start at multiples of 64): one lookup
+      const int pos0 = block * BLOCK_N;
+      const int page = p.cache.block_table[(long long)slot * p.cache.max_pages + (pos0 >> p.cache.page_shift)];
+      const long long base = (long long)page * p.cache.page_stride +
+                             ((long long)kvh * p.cache.page_size + (pos0 & (p.cache.page_size - 1))) * HD;
 #pragma unroll
-    for (int i = 0; i < PIECES; ++i) {
-      const int idx = tid + i * THREADS;
-      const int row = idx / CHUNKS, ch = idx % CHUNKS;
-      const int pos = block * BLOCK_N + row;
-      ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
-      off[i] = ok[i] ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
+      for (int i = 0; i < PIECES; ++i) {
+        const int idx = tid + i * THREADS;
+        const int row = idx / CHUNKS, ch = idx % CHUNKS;
+        const int pos = pos0 + row;
+        ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
+        off[i] = ok[i] ? base + (long long)row * HD + ch * 8 : 0;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) {
+        const int idx = tid + i * THREADS;
+        const int row = idx / CHUNKS, ch = idx % CHUNKS;
+        const int pos = block * BLOCK_N + row;
+        ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
+        off[i] = ok[i] ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
+      }
     }
 #pragma unroll
     for (int i = 0; i < PIECES; ++i) {
@@ -359,7 +375,8 @@ attention_mma_kernel(AttnParams p) {
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
       float m_use = m_new[h] == -INFINITY ? 0.f : m_new[h];
-      alpha[h] = fast_exp2((m_run[h] - m_use) * c_log2);       // 0 while the row has seen no key
+      // 0 when the row sees its first key; 1 while it has seen none (nothing to rescale, and padding rows stay out of the test below)
+      alpha[h] = m_new[h] == -INFINITY ? 1.f : fast_exp2((m_run[h] - m_use) * c_log2);
       neg_mc[h] = -m_use * c_log2;
       m_run[h] = m_new[h];
     }
@@ -375,10 +392,12 @@ attention_mma_kernel(AttnParams p) {
       }
 #pragma unroll
     for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + l_add[h];
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {       // most blocks leave every maximum where it was
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
-      o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
+      for (int i = 0; i < HD / 8; ++i) {
+        o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
+      }
     }
 
     // ---- O += P V
