@@ -51,8 +51,8 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 // reduced and written.  The first batch is issued before the wait on the previous kernel:
 // weights do not depend on it.
 //
-// NORM: the token operand is not read as bfloat16 but made on the fly from float32 rows X
-// (optionally gathered through `rows`): a[t, k] = bf16(X[t, k] * rsqrt(mean(X[t,:]^2) + eps) * nw[k]),
+// The kernel for at most 8 tokens further down can make the token operand on the fly from float32
+// rows X (optionally gathered through `rows`): a[t, k] = bf16(X[t, k] * rsqrt(mean(X[t,:]^2) + eps) * nw[k]),
 // the RMS norm of hostfog/hfee internal/ggml/ops.go:125-134 fused into the product that follows it.
 struct NormArgs {
   const float* x;        // [*, ldx] float32 rows (A is unused)
@@ -63,15 +63,14 @@ struct NormArgs {
   int add_unit;          // scale by 1 + weight
 };
 
-template <int MT, int NT, int NW, int EPI, bool NORM, typename TOut>
+template <int MT, int NT, int NW, int EPI, typename TOut>
 __global__ void __launch_bounds__(NW * 32, 2048 / (NW * 32) >= 4 ? 2 : 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
-                   long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K, NormArgs norm) {
+                   long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
   constexpr int ROWS = 8 * NT;
   constexpr int UNROLL = LOADS_IN_FLIGHT / NT;     // k32-steps per batch of loads
   constexpr int STRIDE = NW * UNROLL;              // k32-steps all warps cover per batch
   __shared__ float red[NW][MT * 16][ROWS + 1];
-  __shared__ float inv_rms[NORM ? MT * 16 : 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
 
@@ -90,8 +89,6 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
       for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
   const __nv_bfloat16* arow[MT][2];
-  const float* xrow[MT][2];
-  float asc[MT][2];
   bool aok[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -100,8 +97,6 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
       int t = mt * 16 + h * 8 + g;
       aok[mt][h] = t < M;
       arow[mt][h] = A + (long long)(aok[mt][h] ? t : 0) * lda;
-      xrow[mt][h] = nullptr;
-      asc[mt][h] = 0.f;
     }
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -130,36 +125,10 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (s0 + u * NW) * 32 + c * 8;
       const bool kok = k < K;
-      float4 nw0 = make_float4(0.f, 0.f, 0.f, 0.f), nw1 = nw0;
-      if constexpr (NORM) {
-        if (kok) {
-          nw0 = __ldg((const float4*)(norm.weight + k));
-          nw1 = __ldg((const float4*)(norm.weight + k + 4));
-          if (norm.add_unit) {
-            nw0.x += 1.f; nw0.y += 1.f; nw0.z += 1.f; nw0.w += 1.f;
-            nw1.x += 1.f; nw1.y += 1.f; nw1.z += 1.f; nw1.w += 1.f;
-          }
-        }
-      }
-      auto normed = [&](const float* row, float sc) {
-        float4 x0 = __ldg((const float4*)(row + k)), x1 = __ldg((const float4*)(row + k + 4));
-        uint4 r;
-        r.x = pack2(x0.x * sc * nw0.x, x0.y * sc * nw0.y);
-        r.y = pack2(x0.z * sc * nw0.z, x0.w * sc * nw0.w);
-        r.z = pack2(x1.x * sc * nw1.x, x1.y * sc * nw1.y);
-        r.w = pack2(x1.z * sc * nw1.z, x1.w * sc * nw1.w);
-        return r;
-      };
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        uint4 lo, hi;
-        if constexpr (NORM) {
-          lo = (kok && aok[mt][0]) ? normed(xrow[mt][0], asc[mt][0]) : zero;
-          hi = (kok && aok[mt][1]) ? normed(xrow[mt][1], asc[mt][1]) : zero;
-        } else {
-          lo = (kok && aok[mt][0]) ? __ldg((const uint4*)(arow[mt][0] + k)) : zero;
-          hi = (kok && aok[mt][1]) ? __ldg((const uint4*)(arow[mt][1] + k)) : zero;
-        }
+        const uint4 lo = (kok && aok[mt][0]) ? __ldg((const uint4*)(arow[mt][0] + k)) : zero;
+        const uint4 hi = (kok && aok[mt][1]) ? __ldg((const uint4*)(arow[mt][1] + k)) : zero;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, src[u][nt].x, src[u][nt].y);
@@ -215,33 +184,6 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
   load_batch(0, 0, 0, wv[0]);
   pdl_wait();
   pdl_launch_dependents();
-  if constexpr (NORM) {
-    // 1/rms of every token row: warp w takes tokens w, w+NW, ...; fixed order, so a row's
-    // scale does not depend on the batch
-    for (int t = warp; t < MT * 16; t += NW) {
-      float ss = 0.f;
-      if (t < M) {
-        const float* xr = norm.x + (long long)(norm.rows ? norm.rows[t] : t) * norm.ldx;
-        for (int k = lane * 4; k < K; k += 128) {
-          float4 v = __ldg((const float4*)(xr + k));
-          ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-        }
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) inv_rms[t] = t < M ? 1.0f / sqrtf(ss / (float)K + norm.eps) : 0.f;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        int t = mt * 16 + h * 8 + g;
-        if (aok[mt][h]) {
-          xrow[mt][h] = norm.x + (long long)(norm.rows ? norm.rows[t] : t) * norm.ldx;
-          asc[mt][h] = inv_rms[t];
-        }
-      }
-  }
   int tile_no = 0, in_tile = 0;                 // of the batch being computed
   auto next = [&](int& t, int& b) { if (++b == bpt) { b = 0; ++t; } };
   for (int j = 0; j < total; j += 2) {
@@ -612,9 +554,9 @@ int launch_slices(const void* A, long long lda, const void* W, long long ldw, vo
   return hfee_check_launch("gemm_stream_slices");
 }
 
-template <int MT, int NT, int NW, bool NORM>
+template <int MT, int NT, int NW>
 int launch(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
-           int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
+           int epilogue, int M, int N, int K, cudaStream_t stream) {
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   static int resident = 0;                       // CTAs of this instantiation the whole GPU holds at once
@@ -622,12 +564,12 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
     int dev = 0, sms = 0, per_sm = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<MT, NT, NW, EPI_STORE, NORM, float>, NW * 32, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<MT, NT, NW, EPI_STORE, float>, NW * 32, 0);
     resident = (sms > 0 ? sms : 148) * (per_sm > 0 ? per_sm : 1);
   }
   int n_tiles = (N + 8 * NT - 1) / (8 * NT);
   unsigned grid = (unsigned)(n_tiles < resident ? n_tiles : resident);
-#define HFEE_GO(EPI, T) hfee_launch(gemm_stream_kernel<MT, NT, NW, EPI, NORM, T>, dim3(grid), dim3(NW * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K, norm)
+#define HFEE_GO(EPI, T) hfee_launch(gemm_stream_kernel<MT, NT, NW, EPI, T>, dim3(grid), dim3(NW * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K)
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
     HFEE_GO(EPI_ACCUM, float);
@@ -667,12 +609,11 @@ int launch_rows(const void* A, long long lda, const void* W, long long ldw, void
 // Enough 8-row tiles to give every resident warp (148 SMs x 16) about one: a warp per tile.
 constexpr int ROWS_MIN_TILES = 1536;
 
-template <bool NORM>
 int by_tokens(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
-              int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
-  if (M <= 16) return launch<1, 1, 16, NORM>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
-  if (M <= 32) return launch<2, 2, 8, NORM>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
-  return launch<4, 4, 4, NORM>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
+              int epilogue, int M, int N, int K, cudaStream_t stream) {
+  if (M <= 16) return launch<1, 1, 16>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  if (M <= 32) return launch<2, 2, 8>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
+  return launch<4, 4, 4>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
 }
 
 int check_common(const void* W, long long ldw, long long ldc, int epilogue, int M, int N, int K) {
@@ -701,19 +642,21 @@ HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long 
     if (M <= 16) return launch_rows<1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
     return launch_rows<2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
   }
-  return by_tokens<false>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, none, stream);
+  return by_tokens(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
 }
 
-// The same with the RMS norm of float32 rows X fused in front: tokens = bf16(norm(X[rows])).
+// The same with the RMS norm of float32 rows X fused in front: tokens = bf16(norm(X[rows])).  For at
+// most 8 tokens and K <= 2048 (the kernel that keeps the tokens in registers); other shapes are
+// refused: run the norm kernel and hfee_gemm_stream instead.
 HFEE_API int hfee_gemm_stream_norm(const float* X, long long ldx, const int* rows, const float* norm_weight,
                                    float eps, int add_unit, const void* W, long long ldw, void* C, long long ldc,
                                    int out_dtype, int epilogue, int M, int N, int K, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;
   int rc = check_common(W, ldw, ldc, epilogue, M, N, K);
   if (rc != HFEE_OK) return rc;
+  HFEE_REQUIRE(M <= 8 && K <= SL_PASS, "gemm_stream_norm: the fused norm takes at most 8 tokens and K <= %d (got M=%d, K=%d)", SL_PASS, M, K);
   HFEE_REQUIRE(ldx % 4 == 0 && ldx >= K && (uintptr_t)X % 16 == 0 && (uintptr_t)norm_weight % 16 == 0,
                "gemm_stream_norm: float32 rows need a leading dimension %% 4 == 0 and 16-byte alignment");
   NormArgs norm{X, ldx, rows, norm_weight, eps, add_unit};
-  if (M <= 8 && K <= SL_PASS) return launch_slices<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
-  return by_tokens<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
+  return launch_slices<true>(nullptr, 0, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, norm, stream);
 }

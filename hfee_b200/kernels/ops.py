@@ -305,7 +305,8 @@ def _stream_k_workspace():
 def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,
                      epilogue: int = EPI_STORE, rows: Optional[torch.Tensor] = None, add_unit: bool = False) -> None:
     """:func:`gemm_stream` with the RMS norm fused in front: the token operand is
-    bf16(x[rows] * rsqrt(mean(x^2) + eps) * norm_weight) made on the fly from float32 rows."""
+    bf16(x[rows] * rsqrt(mean(x^2) + eps) * norm_weight) made on the fly from float32 rows.  At most
+    8 rows and a width of at most 2,048 (the kernel that keeps the tokens in registers)."""
     lib = library()
     _i32(rows, "rows")
     k = x.shape[1]
@@ -334,7 +335,7 @@ def _norm_fusable(inp, w: torch.Tensor) -> bool:
     p = inp.fused_params()
     x = inp.source
     return (p is not None and inp.out_dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and inp.n <= STREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and x.shape[1] <= FUSE_NORM_MAX_WIDTH and _rows(x, "x") % 4 == 0
+            and inp.n <= 8 and x.shape[1] % 8 == 0 and x.shape[1] <= FUSE_NORM_MAX_WIDTH and _rows(x, "x") % 4 == 0
             and _rows(w, "w") % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and p[0].data_ptr() % 16 == 0)
 

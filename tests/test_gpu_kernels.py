@@ -229,8 +229,8 @@ def test_sample_greedy_and_temperature(ops, m, v):
             assert got == want or abs(float(cum[where] - cum[at])) / float(cum[-1]) < 1e-9
 
 
-@pytest.mark.parametrize("m", [1, 8, 17, 64])
-@pytest.mark.parametrize("n,k", [(24, 40), (96, 2048), (3072, 2048), (5000, 2056)])
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("n,k", [(24, 40), (96, 2048), (3072, 2048), (5000, 1000)])
 def test_gemm_stream_with_fused_norm(ops, m, n, k):
     """The norm fused in front of the product equals norm kernel + product kernel (same bf16
     rounding of the normed rows), with and without a row gather, for every epilogue."""
