@@ -98,3 +98,4 @@ def test_generation_with_default_options_is_the_same_on_device_and_host(tiny_dir
                        max_cache_tokens=160)
         got = small.generate(prompts, opts)
         assert [r.token_ids for r in got] == host
+        assert sum(r.stats.preemptions for r in got) > 0          # a request came back and its ring was loaded again
