@@ -17,6 +17,25 @@ def test_defaults_are_the_references():
     assert not o.device_only and SamplingOptions(temperature=0.7, top_k=0, top_p=1.0, repeat_penalty=1.0).device_only
 
 
+def test_which_options_the_device_kernels_take():
+    o = SamplingOptions()
+    assert o.device_chain and not o.device_only                        # the reference's defaults: the chain kernels
+    assert SamplingOptions.greedy().device_chain and SamplingOptions.greedy().device_only
+    assert SamplingOptions(temperature=0.0).device_chain                # greedy with the default penalty: k = 1 after the penalty
+    assert not SamplingOptions(top_k=65).device_chain and SamplingOptions(top_k=64).device_chain
+    assert not SamplingOptions(top_k=0).device_chain                    # top-p over all tokens needs the full sort: host
+    assert not SamplingOptions(repeat_last_n=-1).device_chain and not SamplingOptions(repeat_last_n=257).device_chain
+    assert SamplingOptions(repeat_last_n=256).device_chain and SamplingOptions(repeat_last_n=0, top_k=5).device_chain
+
+
+def test_equal_logits_are_taken_in_the_order_of_their_ids():
+    logits = np.zeros(50, dtype=np.float32)
+    logits[[40, 7, 23]] = 3.0
+    o = SamplingOptions(temperature=1.0, top_k=2, top_p=1.0, repeat_penalty=1.0)
+    # the two candidates are ids 7 and 23 (not 40), each with probability one half, 7 first
+    assert [sample_host(logits, [], o, u) for u in (0.1, 0.49, 0.51, 0.99)] == [7, 7, 23, 23]
+
+
 def test_uniform_is_a_pure_function_in_unit_interval():
     xs = [uniform(3, 0, i) for i in range(2000)]
     assert all(0 <= x < 1 for x in xs) and abs(np.mean(xs) - 0.5) < 0.03
