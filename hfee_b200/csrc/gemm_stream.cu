@@ -527,6 +527,148 @@ gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, co
   }
 }
 
+// 9 to 16 tokens, K of at most 2,048: one CTA of 16 warps per SM; warp w owns columns [128 w, 128 w + 128)
+// and keeps both halves of the MMA's token tile for them in registers (32 registers), with four batches
+// of four weight loads in flight.  Half as many CTAs as above read the tokens, so the token traffic (every
+// CTA reads all of it) stays what it is for 8 tokens.
+constexpr int WD_WARPS = 16;
+constexpr int WD_STEPS = 4;
+constexpr int WD_SLICE = WD_STEPS * 32;                  // 128 columns per warp
+constexpr int WD_DEPTH = 4;
+
+template <int EPI, typename TOut>
+__global__ void __launch_bounds__(WD_WARPS * 32, 1)
+gemm_stream_wide_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W,
+                        long long ldw, TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  extern __shared__ __align__(16) float red_raw[];       // [WD_WARPS][16][SL_TOKEN_PITCH]
+  float (*red)[16][SL_TOKEN_PITCH] = reinterpret_cast<float (*)[16][SL_TOKEN_PITCH]>(red_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int n_tiles = (N + 7) / 8;
+  const int t_begin = (int)((long long)blockIdx.x * n_tiles / gridDim.x);
+  const int total = (int)((long long)(blockIdx.x + 1) * n_tiles / gridDim.x) - t_begin;      // one pass: a unit is a tile
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 wv[WD_DEPTH][WD_STEPS];
+  const int k0 = warp * WD_SLICE + c * 8;
+  auto load_unit = [&](int unit, uint4 (&dst)[WD_STEPS]) {
+    const int r = (t_begin + unit) * 8 + g;
+    const bool rok = unit < total && r < N;
+    const __nv_bfloat16* wrow = W + (long long)(rok ? r : 0) * ldw + k0;
+#pragma unroll
+    for (int u = 0; u < WD_STEPS; ++u) dst[u] = (rok && k0 + u * 32 < K) ? ld_stream(wrow + u * 32) : zero;
+  };
+#pragma unroll
+  for (int d = 0; d < WD_DEPTH - 1; ++d) load_unit(d, wv[d]);
+  pdl_wait();
+  pdl_launch_dependents();
+
+  uint4 a_lo[WD_STEPS], a_hi[WD_STEPS];
+  {
+    const bool lo_ok = g < M, hi_ok = g + 8 < M;
+    const __nv_bfloat16* row_lo = A + (long long)(lo_ok ? g : 0) * lda + k0;
+    const __nv_bfloat16* row_hi = A + (long long)(hi_ok ? g + 8 : 0) * lda + k0;
+#pragma unroll
+    for (int u = 0; u < WD_STEPS; ++u) {
+      a_lo[u] = (lo_ok && k0 + u * 32 < K) ? __ldg((const uint4*)(row_lo + u * 32)) : zero;
+      a_hi[u] = (hi_ok && k0 + u * 32 < K) ? __ldg((const uint4*)(row_hi + u * 32)) : zero;
+    }
+  }
+
+  auto group_size = [&](int grp) { return min(SL_GROUP, total - grp * SL_GROUP); };
+  auto finish_group = [&](int grp) {
+    const int gs = group_size(grp);
+    const int t0 = t_begin + grp * SL_GROUP;
+    if constexpr (EPI == EPI_SWIGLU) {
+      const int t = threadIdx.x >> 5, o = threadIdx.x & 31;             // 16 tokens x 32 outputs = 512 threads
+      const int tile = o >> 2, i = o & 3;
+      const long long col = (long long)(t0 + tile) * 4 + i;
+      if (t < M && tile < gs && col < N / 2) {
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < WD_WARPS; ++w) { gate += red[w][t][tile * 8 + i]; up += red[w][t][tile * 8 + 4 + i]; }
+        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = (threadIdx.x >> 6) + h * 8, o = threadIdx.x & 63;  // 16 tokens x 64 columns = 2 x 512
+        const long long col = (long long)t0 * 8 + o;
+        if (t < M && o < gs * 8 && col < N) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < WD_WARPS; ++w) v += red[w][t][o];
+          const long long at = (long long)t * ldc + col;
+          if constexpr (EPI == EPI_ACCUM) C[at] = to_f32<TOut>(C[at]) + v;
+          else C[at] = from_f32<TOut>(v);
+        }
+      }
+    }
+  };
+  auto process = [&](int unit, const uint4 (&src)[WD_STEPS]) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < WD_STEPS; ++u) {
+      mma_bf16(acc, a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, src[u].x, src[u].y);
+      mma_bf16(acc, a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, src[u].z, src[u].w);
+    }
+    const int tig = unit % SL_GROUP, grp = unit / SL_GROUP;
+    *reinterpret_cast<float2*>(&red[warp][g][tig * 8 + 2 * c]) = make_float2(acc[0], acc[1]);
+    *reinterpret_cast<float2*>(&red[warp][g + 8][tig * 8 + 2 * c]) = make_float2(acc[2], acc[3]);
+    if (tig == group_size(grp) - 1) {
+      __syncthreads();
+      finish_group(grp);
+      __syncthreads();                                   // the sums have been read: the next group may overwrite them
+    }
+  };
+
+  for (int j = 0; j < total; j += WD_DEPTH) {
+#pragma unroll
+    for (int d = 0; d < WD_DEPTH; ++d) {
+      if (j + d < total) {
+        load_unit(j + d + WD_DEPTH - 1, wv[(d + WD_DEPTH - 1) % WD_DEPTH]);
+        process(j + d, wv[d]);
+      }
+    }
+  }
+}
+
+int launch_wide(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
+                int epilogue, int M, int N, int K, cudaStream_t stream) {
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int n_tiles = (N + 7) / 8;
+  unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
+  constexpr int RED_BYTES = WD_WARPS * 16 * SL_TOKEN_PITCH * 4;
+#define HFEE_GO(EPI, T)                                                                                                   \
+  do {                                                                                                                    \
+    static bool configured = false;                                                                                       \
+    if (!configured) {                                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(gemm_stream_wide_kernel<EPI, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, RED_BYTES); \
+      if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "gemm_stream: cannot get shared memory: %s", cudaGetErrorString(e)); \
+      configured = true;                                                                                                  \
+    }                                                                                                                     \
+    hfee_launch(gemm_stream_wide_kernel<EPI, T>, dim3(grid), dim3(WD_WARPS * 32), RED_BYTES, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K); \
+  } while (0)
+  if (epilogue == EPI_ACCUM) {
+    if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");
+    HFEE_GO(EPI_ACCUM, float);
+  } else if (epilogue == EPI_SWIGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
+  }
+#undef HFEE_GO
+  return hfee_check_launch("gemm_stream_wide");
+}
+
 template <bool NORM>
 int launch_slices(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int out_dtype,
                   int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
@@ -638,6 +780,7 @@ HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long 
                "gemm_stream: the tokens' leading dimension %lld must be a multiple of 8, at least K, and 16-byte aligned", lda);
   NormArgs none{nullptr, 0, nullptr, nullptr, 0.f, 0};
   if (M <= 8) return launch_slices<false>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, none, stream);
+  if (M <= 16 && K <= WD_WARPS * WD_SLICE) return launch_wide(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
   if ((N + 7) / 8 >= ROWS_MIN_TILES && M <= 32) {
     if (M <= 16) return launch_rows<1>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);
     return launch_rows<2>(A, lda, W, ldw, C, ldc, out_dtype, epilogue, M, N, K, stream);

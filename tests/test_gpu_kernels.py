@@ -153,7 +153,7 @@ def test_gemm_simt_rows_do_not_depend_on_batch(ops):
     assert torch.equal(one[0], full[41])
 
 
-@pytest.mark.parametrize("m", [1, 2, 8, 9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 12, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(8, 8), (24, 40), (100, 96), (2048, 2048), (257, 1000), (264, 4104), (20004, 520)])
 def test_gemm_stream(ops, m, n, k):
     g = torch.Generator().manual_seed(6)
@@ -173,7 +173,7 @@ def test_gemm_stream(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 8, 9, 16, 20, 64])
-@pytest.mark.parametrize("inner,k", [(4, 8), (172, 64), (1000, 96), (8192, 256), (10004, 4104)])
+@pytest.mark.parametrize("inner,k", [(4, 8), (172, 64), (1000, 96), (8192, 256), (1028, 2048), (10004, 4104)])
 def test_gemm_stream_swiglu(ops, m, inner, k):
     g = torch.Generator().manual_seed(7)
     a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
