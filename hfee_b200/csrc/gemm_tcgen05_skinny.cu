@@ -127,6 +127,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weights are not the previous kernel's output: the weight tiles of the first round of the
+      // ring (all stages are free) are requested before the wait, their token tiles after it.
+      uint32_t pre = 0;
+      for (int i = blockIdx.x; i < items && pre < (uint32_t)STAGES; i += gridDim.x) {
+        const int n0 = (i % a.w_tiles) * WM, split = i / a.w_tiles;
+        const int kb0 = split * a.kb_per_split, kb1 = min(a.k_blocks, kb0 + a.kb_per_split);
+        for (int kb = kb0; kb < kb1 && pre < (uint32_t)STAGES; ++kb, ++pre) {
+          mbar_expect_tx(&full_bar[pre], Cfg::STAGE_BYTES);
+          tma_load_2d(tiles + pre * Cfg::STAGE_BYTES, &map_w, kb * BK, n0, &full_bar[pre]);
+        }
+      }
       pdl_wait();            // the token tiles are the previous kernel's output
       uint32_t it = 0;
       bool ok = true;
@@ -135,11 +146,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int kb0 = split * a.kb_per_split, kb1 = min(a.k_blocks, kb0 + a.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
-          ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag);
-          if (!ok) break;
           unsigned char* w_dst = tiles + s * Cfg::STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-          tma_load_2d(w_dst, &map_w, kb * BK, n0, &full_bar[s]);
+          if (it >= pre) {
+            ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag);
+            if (!ok) break;
+            mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+            tma_load_2d(w_dst, &map_w, kb * BK, n0, &full_bar[s]);
+          }
           tma_load_2d(w_dst + Cfg::W_BYTES, &map_a, kb * BK, 0, &full_bar[s]);
         }
       }
@@ -212,7 +225,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
-// C (+)= sum over splits (in split order) of the partial tiles, with the epilogue applied.
+// C (+)= sum over splits (in split order) of the partial tiles, with the epilogue applied.  The
+// partial values of up to eight splits are requested together and then added in split order.
+constexpr int RED_BATCH = 8;
+
 template <int EPI, typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restrict__ C, long long ldc, int M, int N,
                                      int splits) {
@@ -222,21 +238,36 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restr
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)M * out_cols) return;
   const int t = (int)(idx / out_cols), c = (int)(idx % out_cols);
+  const long long split_pitch = (long long)M * N;
   if constexpr (EPI == EPI_SWIGLU) {
-    const int gcol = (c >> 2) * 8 + (c & 3);
+    const float* p = ws + (long long)t * N + (c >> 2) * 8 + (c & 3);
     float gate = 0.f, up = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* p = ws + ((long long)s * M + t) * N;
-      gate += p[gcol];
-      up += p[gcol + 4];
+    for (int s0 = 0; s0 < splits; s0 += RED_BATCH) {
+      float g[RED_BATCH], u[RED_BATCH];
+#pragma unroll
+      for (int j = 0; j < RED_BATCH; ++j) {
+        const bool ok = s0 + j < splits;
+        g[j] = ok ? p[(s0 + j) * split_pitch] : 0.f;
+        u[j] = ok ? p[(s0 + j) * split_pitch + 4] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < RED_BATCH; ++j) { gate += g[j]; up += u[j]; }
     }
     C[(long long)t * ldc + c] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
   } else {
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) v += ws[((long long)s * M + t) * N + c];
+    const float* p = ws + (long long)t * N + c;
     const long long o = (long long)t * ldc + c;
-    if constexpr (EPI == EPI_ACCUM) v += to_f32<TOut>(C[o]);
-    C[o] = from_f32<TOut>(v);
+    float old = 0.f;
+    if constexpr (EPI == EPI_ACCUM) old = to_f32<TOut>(C[o]);
+    float v = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += RED_BATCH) {
+      float part[RED_BATCH];
+#pragma unroll
+      for (int j = 0; j < RED_BATCH; ++j) part[j] = s0 + j < splits ? p[(s0 + j) * split_pitch] : 0.f;
+#pragma unroll
+      for (int j = 0; j < RED_BATCH; ++j) v += part[j];
+    }
+    C[o] = from_f32<TOut>(v + old);
   }
 }
 
