@@ -456,12 +456,13 @@ MAX_SPLITS = 32
 
 
 def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
-    """How many CTAs share the keys of one (request, kv head) in a decode step: enough to give
-    every SM the three CTAs it can hold at head size 64, and at least four even when the batch
-    alone would fill the GPU (shorter CTAs balance better and keep more loads in flight: measured
-    at 2,048 keys, batch 32: 41.8 us unsplit, 33.4 us with four), but at least two key blocks of
-    64 each."""
-    want = max(4, 3 * SM_COUNT // max(1, requests * kv_heads))
+    """How many CTAs share the keys of one (request, kv head) in a decode step: about four CTAs
+    per SM in all (measured alone at batch 8: 9 splits against 6 take 10.3 / 27.2 / 90.8 us against
+    11.3 / 30.9 / 99.6 us at 2,048 / 8,192 / 32,768 keys; batch 12 at 8,192 keys: 6 against 4 take
+    37.5 against 42.6 us), and at least four even when the batch alone would fill the GPU (shorter
+    CTAs balance better and keep more loads in flight: at 2,048 keys, batch 32: 41.8 us unsplit,
+    33.4 us with four), but at least two key blocks of 64 each."""
+    want = max(4, 4 * SM_COUNT // max(1, requests * kv_heads))
     return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 
