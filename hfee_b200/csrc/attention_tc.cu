@@ -1,19 +1,29 @@
-// Causal grouped-query flash attention for prompt portions on the 5th-generation tensor cores:
-// S = Q K^T and O_block = P V are tcgen05 MMAs with their accumulators in tensor memory, Q/K/V
-// tiles arrive by TMA (K and V page by page through the block table), and a warpgroup of four
-// softmax warps owns one query row per thread (so row maxima and sums need no shuffles).
+// Causal grouped-query flash attention for prompt portions on the 5th-generation tensor cores,
+// head sizes 64 and 128.
 //
-// A CTA serves one (request, kv head, tile of 128 query rows); the rows are (token, query head of
-// the group) pairs, so the group shares every key/value tile.  Keys go in blocks of 128:
-//   warp 0     TMA producer   Q once; per block K and V (two 64-key page pieces each) into a
-//                             3-stage ring
-//   warp 1     MMA issuer     S_j = Q K_j^T into S buffer j%2 (issued one block ahead), then
-//                             O_j = P_j V_j into O buffer j%2 once the softmax warps wrote P_j
-//   warps 2-5  softmax        read S_j from TMEM (twice: row max, then exponentials), write P_j as
-//                             bf16 into 128B-swizzled shared memory, keep the running max/sum and
-//                             the output row in registers: o = o * alpha_j + O_j, read from TMEM
-// Masks: causal and window, applied only in blocks that need them.  Head size 64, pages of at least
-// 64 tokens (a power of two); other shapes use the mma.sync kernel.  Every barrier wait is bounded.
+// A CTA serves one (request, kv head) and NT tiles of 128 query rows; the rows are (token, query
+// head of the group) pairs, so the whole group shares every key/value tile, and the NT tiles
+// (adjacent token ranges) share them too.  Keys go in blocks of 128:
+//   warp 0        TMA producer   Q tiles once; per block K then V (64-key page pieces through the
+//                                block table, 64 head dims per load) into a ring of stages
+//   warp 1        MMA issuer     S_t = Q_t K^T into tile t's 128 S columns of tensor memory, then,
+//                                once tile t's softmax warps have turned S_t into P_t,
+//                                O_t += P_t V with P_t read from tensor memory (it overwrites the
+//                                first 64 columns of S_t as packed bfloat16) and directly the next
+//                                S_t: while one tile's rows are in the softmax the tensor core
+//                                works for the other tile
+//   warps 4..     softmax        a warpgroup per tile, one query row per thread: the row of S is read
+//                                from tensor memory once, max / exp2 / sum in registers, P written
+//                                back with tcgen05.st (warps 2 and 3 only give their registers to
+//                                the softmax warpgroups)
+// O_t stays in tensor memory for the whole key loop (the MMA accumulates into it).  The running row
+// maximum is moved only when it grew by more than 2^8 in the exponent (then that warp rescales its
+// O rows in tensor memory); otherwise the old maximum keeps being used for P and for the row sum,
+// which cancels in O / sum.
+// Masks: causal and window, applied only in blocks that need them; V rows of positions behind the
+// last token of the CTA are cleared in shared memory, so that whatever an earlier owner of the page
+// left there (also a NaN) meets no MMA.  Pages of at least 64 tokens (a power of two); other shapes
+// use the mma.sync kernel.  Every barrier wait is bounded.
 // Reference: hostfog/hfee internal/llm/forward.go:146-178, internal/ggml/ops.go:136-150.
 #include "tcgen05.cuh"
 
@@ -21,19 +31,26 @@ namespace {
 
 using namespace tc;
 
-constexpr int QM = 128;            // query rows per CTA
+constexpr int QM = 128;            // query rows per tile
 constexpr int KB = 128;            // keys per block
-constexpr int HD = 64;             // head size
-constexpr int KV_STAGES = 2;
-constexpr int NBUF = 1;            // S, P and O buffers per CTA; two CTAs share an SM and overlap each other
-constexpr int AT_THREADS = 192;
-constexpr int Q_BYTES = QM * HD * 2;            // 16 KB
-constexpr int KT_BYTES = KB * HD * 2;           // 16 KB each for K and V
-constexpr int P_BYTES = QM * KB * 2;            // 32 KB: two slabs of [128 rows][64 keys]
-constexpr int TILE_BYTES = Q_BYTES + KV_STAGES * 2 * KT_BYTES + NBUF * P_BYTES;
-constexpr int AT_SMEM = TILE_BYTES + 256;       // + barriers; the base must come 1024-aligned (checked)
-constexpr uint32_t TMEM_COLS = NBUF == 1 ? 256 : 512;     // S: NBUF x 128 columns, O: NBUF x 64 columns
-constexpr uint32_t S_COL = 0, O_COL = NBUF * KB;
+constexpr int SLAB_BYTES = 128 * 128;   // 128 rows of 64 bf16: one 128-byte-swizzled slab of Q, K or V
+constexpr float RESCALE_LOG2 = 8.f;     // the row maximum moves only when it grew by more than this
+
+template <int HD, int NT>
+struct TcCfg {
+  static constexpr int SLABS = HD / 64;
+  static constexpr int Q_BYTES = QM * HD * 2;              // one query tile
+  static constexpr int KT_BYTES = KB * HD * 2;             // K or V of one key block
+  static constexpr int STAGES = HD == 64 ? 3 : 2;
+  static constexpr int TILE_BYTES = NT * Q_BYTES + STAGES * 2 * KT_BYTES;
+  static constexpr int SMEM = TILE_BYTES + 256;            // + barriers; the base must come 1024-aligned (checked)
+  static constexpr int THREADS = 128 + NT * 128;      // warpgroup 0: producer and MMA warps; one warpgroup per tile
+  static constexpr uint32_t S_COL = 0, O_COL = NT * KB;    // S_t at t*128, O_t at O_COL + t*HD
+  static constexpr uint32_t TMEM_COLS = NT * (KB + HD) <= 256 ? 256 : 512;
+  static constexpr int N_BARS = NT + 3 * STAGES + 3 * NT + 1;
+  static_assert(N_BARS * 8 + 8 <= 256, "barrier area");
+  static_assert(SMEM <= 227 * 1024, "shared memory");
+};
 
 struct TcAttnParams {
   __nv_bfloat16* out; int ld_o;
@@ -44,7 +61,7 @@ struct TcAttnParams {
   int heads, group;
   float scale_log2;
   int window;
-  int tokens_per_tile, q_tiles;
+  int tokens_per_tile, q_tiles, q_groups;      // q_groups = CTAs along the tokens = ceil(q_tiles / NT)
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -55,70 +72,110 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, i
       : "memory");
 }
 
-// Descriptor of an MN-major operand tile in the 128-byte swizzle: rows (the K index) are 128 bytes
-// of 64 contiguous MN elements, 8-row groups are `sbo` bytes apart; `lbo` is the distance between
-// 64-element chunks along MN (unused when the tile is 64 wide).
+// Descriptor of an MN-major operand tile, 64 MN elements wide, in the 128-byte swizzle: rows (the K
+// index) are 128 bytes of 64 contiguous MN elements, 8-row groups are `sbo` bytes apart.
 __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
   return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
          (1ull << 46) | (2ull << 61);
 }
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 bf16, two to a 32-bit column) comes from
+// tensor memory.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+template <int HD, int NT>
+__global__ void __launch_bounds__(TcCfg<HD, NT>::THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, TcAttnParams p, int* __restrict__ status) {
-  // no static shared memory: tiles first (1024-byte aligned for the swizzle), barriers behind them,
-  // so that two CTAs fit one SM
+  using C = TcCfg<HD, NT>;
+  constexpr int ST = C::STAGES;
+  // no static shared memory: tiles first (1024-byte aligned for the swizzle), barriers behind them
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char* base = smem_dyn;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base + TILE_BYTES);
-  uint64_t& q_full = bars[0];
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = kv_full + KV_STAGES;
-  uint64_t* s_full = kv_empty + KV_STAGES;
-  uint64_t* s_empty = s_full + NBUF;
-  uint64_t* p_full = s_empty + NBUF;
-  uint64_t* p_empty = p_full + NBUF;
-  uint64_t* o_full = p_empty + NBUF;
-  uint64_t* o_empty = o_full + NBUF;
-  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(o_empty + NBUF);
-  int& abort_flag = *reinterpret_cast<int*>(reinterpret_cast<uint32_t*>(o_empty + NBUF) + 1);
-  static_assert((1 + 2 * KV_STAGES + 6 * NBUF) * 8 + 8 <= 256, "barrier area");
-  unsigned char* q_s = base;
-  unsigned char* kv_s = base + Q_BYTES;                                 // [stage][K | V]
-  unsigned char* p_s = kv_s + KV_STAGES * 2 * KT_BYTES;                 // [2][P]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + C::TILE_BYTES);
+  uint64_t* q_full = bars;                 // [NT]
+  uint64_t* k_full = q_full + NT;          // [ST]
+  uint64_t* v_full = k_full + ST;          // [ST]
+  uint64_t* kv_empty = v_full + ST;        // [ST]
+  uint64_t* s_full = kv_empty + ST;        // [NT]  S_t of the current block is in tensor memory
+  uint64_t* p_full = s_full + NT;          // [NT]  P_t is in tensor memory (and O_t rescaled if it had to be)
+  uint64_t* o_done = p_full + NT;          // [NT]  the MMAs O_t += P_t V of the current block have completed
+  uint64_t* v_clean = o_done + NT;         //       the last block's V rows behind the last position are cleared
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(v_clean + 1);
+  int& abort_flag = *reinterpret_cast<int*>(reinterpret_cast<uint32_t*>(v_clean + 1) + 1);
+  unsigned char* q_s = base;                                  // [NT][slab][128 rows][64]
+  unsigned char* kv_s = base + NT * C::Q_BYTES;               // [stage][K | V][slab][128 keys][64]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // CTAs start in the order of blockIdx.x, then y: the heaviest tiles (latest positions) of every
   // kv head first, the light ones last, so that they fill the gaps at the end
-  const int tile = p.q_tiles - 1 - (int)blockIdx.y, kvh = blockIdx.x, r = blockIdx.z;
+  const int qg = p.q_groups - 1 - (int)blockIdx.y, kvh = blockIdx.x, r = blockIdx.z;
   const int tok0 = p.cu_tokens[r], n_new = p.cu_tokens[r + 1] - tok0;
-  const int t_first = tile * p.tokens_per_tile;
-  if (t_first >= n_new) return;
-  const int t_count = min(p.tokens_per_tile, n_new - t_first);
+  if (qg * NT * p.tokens_per_tile >= n_new) return;
   const int slot = p.slots[r], before = p.context_before[r];
-  const int pos_first = before + t_first, pos_last = pos_first + t_count - 1;
-  const int key_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
-  const int b_lo = key_lo / KB, nb = pos_last / KB - b_lo + 1;
+  // per tile: first token, token count, key blocks; all tiles walk the blocks from the first one
+  // that the earliest tile can see
+  int t_first[NT], t_count[NT], nb_t[NT];
+  int nb = 0, pos_last_all = 0;
+  const int pos_first0 = before + qg * NT * p.tokens_per_tile;
+  const int key_lo = (p.window > 0 && pos_first0 + 1 > p.window) ? pos_first0 + 1 - p.window : 0;
+  const int b_lo = key_lo / KB;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    t_first[t] = (qg * NT + t) * p.tokens_per_tile;
+    t_count[t] = min(p.tokens_per_tile, n_new - t_first[t]);
+    nb_t[t] = 0;
+    if (t_count[t] > 0) {
+      const int pos_last = before + t_first[t] + t_count[t] - 1;
+      nb_t[t] = pos_last / KB - b_lo + 1;
+      nb = nb_t[t];
+      pos_last_all = pos_last;
+    }
+  }
 
   if (threadIdx.x == 0) {
     abort_flag = (smem_u32(base) & 1023u) != 0 ? 1 : 0;       // misaligned tiles would corrupt the swizzle
-    mbar_init(&q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int b = 0; b < NBUF; ++b) {
-      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
-      mbar_init(&p_full[b], 4); mbar_init(&p_empty[b], 1);
-      mbar_init(&o_full[b], 1); mbar_init(&o_empty[b], 4);
+    for (int t = 0; t < NT; ++t) {
+      mbar_init(&q_full[t], 1);
+      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1);
     }
+    for (int s = 0; s < ST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(v_clean, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -127,213 +184,248 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();                       // queries and this step's keys/values come from the previous kernels
   pdl_launch_dependents();
+  // the softmax threads hold a whole row of S: they take the registers the first warpgroup does not need
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {
-      // the box is tokens_per_tile x group rows (fewer than 128 when the group does not divide 128;
-      // the rows left over are never read back)
-      mbar_expect_tx(&q_full, (uint32_t)(p.tokens_per_tile * p.group * HD * 2));
-      tma_load_4d(q_s, &map_q, 0, 0, kvh, tok0 + t_first, &q_full);
+      // a query box is tokens_per_tile x group rows (fewer than 128 when the group does not divide
+      // 128; the rows left over are never read back), 64 head dims per load
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        if (nb_t[t] == 0) continue;
+        mbar_expect_tx(&q_full[t], (uint32_t)(p.tokens_per_tile * p.group * HD * 2));
+#pragma unroll
+        for (int h = 0; h < C::SLABS; ++h)
+          tma_load_4d(q_s + t * C::Q_BYTES + h * SLAB_BYTES, &map_q, h * 64, 0, kvh, tok0 + t_first[t], &q_full[t]);
+      }
       bool ok = true;
       for (int j = 0; j < nb && ok; ++j) {
-        const int s = j % KV_STAGES;
-        ok = mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1u) ^ 1u, &abort_flag);
+        const int s = j % ST;
+        ok = mbar_wait(&kv_empty[s], ((j / ST) & 1u) ^ 1u, &abort_flag);
         if (!ok) break;
-        unsigned char* k_dst = kv_s + s * 2 * KT_BYTES;
-        mbar_expect_tx(&kv_full[s], 2 * KT_BYTES);
+        int page[2], in_page[2];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {                       // two pieces of 64 keys
           const int key0 = (b_lo + j) * KB + c * 64;
           // a piece beyond the pages the request holds reads page -1: out of range, zero-filled
-          const int page = (key0 >> p.page_shift) < p.max_pages
-                               ? p.block_table[(long long)slot * p.max_pages + (key0 >> p.page_shift)] : -1;
-          const int in_page = key0 & (p.page_size - 1);
-          tma_load_4d(k_dst + c * (KT_BYTES / 2), &map_k, 0, in_page, kvh, page, &kv_full[s]);
-          tma_load_4d(k_dst + KT_BYTES + c * (KT_BYTES / 2), &map_v, 0, in_page, kvh, page, &kv_full[s]);
+          page[c] = (key0 >> p.page_shift) < p.max_pages
+                        ? p.block_table[(long long)slot * p.max_pages + (key0 >> p.page_shift)] : -1;
+          in_page[c] = key0 & (p.page_size - 1);
         }
+        unsigned char* k_dst = kv_s + s * 2 * C::KT_BYTES;
+        mbar_expect_tx(&k_full[s], C::KT_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int h = 0; h < C::SLABS; ++h)
+            tma_load_4d(k_dst + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_k, h * 64, in_page[c], kvh, page[c], &k_full[s]);
+        mbar_expect_tx(&v_full[s], C::KT_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int h = 0; h < C::SLABS; ++h)
+            tma_load_4d(k_dst + C::KT_BYTES + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_v, h * 64, in_page[c], kvh,
+                        page[c], &v_full[s]);
       }
+    }
+    __syncwarp();
+    // The last block's V rows of positions behind the CTA's last token: their P is zero, but a page
+    // that another request used before may hold anything there, and 0 * NaN is NaN.  Clear them.
+    if (nb > 0) {
+      const int j = nb - 1, s = j % ST;
+      int done = lane == 0 ? (int)mbar_wait(&v_full[s], (j / ST) & 1u, &abort_flag) : 0;
+      done = __shfl_sync(0xffffffffu, done, 0);
+      const int first_row = pos_last_all - (b_lo + j) * KB + 1;       // 1..128
+      if (done && first_row < KB) {
+        unsigned char* v_dst = kv_s + s * 2 * C::KT_BYTES + C::KT_BYTES;
+        const int per_slab = (KB - first_row) * 8;                    // 16-byte pieces
+        for (int i = lane; i < per_slab * C::SLABS; i += 32) {
+          const int h = i / per_slab, o = i % per_slab;
+          *reinterpret_cast<uint4*>(v_dst + h * SLAB_BYTES + first_row * 128 + o * 16) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      __syncwarp();
+      if (lane == 0 && done) mbar_arrive(v_clean);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(QM, KB);                       // A, B K-major
-      constexpr uint32_t idesc_o = make_idesc(QM, HD) | (1u << 16);          // B (V) MN-major
-      const uint32_t q_addr = smem_u32(q_s);
-      bool ok = mbar_wait(&q_full, 0, &abort_flag);
-      auto issue_s = [&](int j) {
-        const int s = j % KV_STAGES, sb = j % NBUF;
-        ok = ok && mbar_wait(&kv_full[s], (j / KV_STAGES) & 1u, &abort_flag);
-        ok = ok && mbar_wait(&s_empty[sb], ((j / NBUF) & 1u) ^ 1u, &abort_flag);
-        if (!ok) return;
-        tc_fence_after();
-        const uint64_t dq = make_desc(q_addr), dk = make_desc(smem_u32(kv_s + s * 2 * KT_BYTES));
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          tc_mma(tmem_base + S_COL + sb * KB, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
-        tc_commit(&s_full[sb]);
+      constexpr uint32_t idesc_o = make_idesc(QM, 64) | (1u << 16);          // B (V) MN-major, 64 head dims per MMA
+      bool ok = true;
+      auto wait = [&](uint64_t* bar, uint32_t parity) {
+        ok = ok && mbar_wait(bar, parity, &abort_flag);
+        return ok;
       };
-      auto issue_pv = [&](int j) {
-        const int s = j % KV_STAGES, sb = j % NBUF;
-        ok = ok && mbar_wait(&p_full[sb], (j / NBUF) & 1u, &abort_flag);
-        ok = ok && mbar_wait(&o_empty[sb], ((j / NBUF) & 1u) ^ 1u, &abort_flag);
-        if (!ok) return;
+      auto issue_s = [&](int t, int j) {
+        const int s = j % ST;
+        if (!wait(&k_full[s], (j / ST) & 1u)) return;
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(p_s + sb * P_BYTES);
-        const uint32_t v_addr = smem_u32(kv_s + s * 2 * KT_BYTES + KT_BYTES);
+        const uint32_t q_addr = smem_u32(q_s + t * C::Q_BYTES), k_addr = smem_u32(kv_s + s * 2 * C::KT_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks / 4) * SLAB_BYTES;          // 16 head dims = 32 bytes further along a slab's rows
+          tc_mma(tmem_base + C::S_COL + t * KB, make_desc(q_addr + off) + 2 * (ks % 4),
+                 make_desc(k_addr + off) + 2 * (ks % 4), idesc_s, ks != 0);
+        }
+        tc_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int j) {
+        const int s = j % ST;
+        if (!wait(&p_full[t], j & 1u)) return;
+        if (!wait(&v_full[s], (j / ST) & 1u)) return;
+        if (j == nb - 1 && !wait(v_clean, 0)) return;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(kv_s + s * 2 * C::KT_BYTES + C::KT_BYTES);
 #pragma unroll
         for (int kk = 0; kk < KB / 16; ++kk) {
-          // P: slab kk/4 of [128 rows][64 keys], 16 keys = 32 bytes further along K
-          const uint64_t dp = make_desc(p_addr + (kk / 4) * (P_BYTES / 2)) + 2 * (kk % 4);
-          // V: 16 keys = two 8-row groups of 1024 bytes further
-          const uint64_t dv = make_desc_mn(v_addr + kk * 2048, 16, 1024);
-          tc_mma(tmem_base + O_COL + sb * HD, dp, dv, idesc_o, kk != 0);
+          // P: 16 keys = 8 columns of packed bf16 further; V: 16 keys = two 8-row groups of 1024 bytes
+#pragma unroll
+          for (int h = 0; h < C::SLABS; ++h)
+            tc_mma_ts(tmem_base + C::O_COL + t * HD + h * 64, tmem_base + C::S_COL + t * KB + kk * 8,
+                      make_desc_mn(v_addr + h * SLAB_BYTES + kk * 2048, 16, 1024), idesc_o, (j > 0 || kk != 0) ? 1u : 0u);
         }
-        tc_commit(&o_full[sb]);
-        tc_commit(&kv_empty[s]);
-        tc_commit(&p_empty[sb]);
+        tc_commit(&o_done[t]);
       };
-      if (ok) issue_s(0);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        if (nb_t[t] > 0) wait(&q_full[t], 0);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        if (nb_t[t] > 0 && ok) issue_s(t, 0);
       for (int j = 0; j < nb && ok; ++j) {
-        if (j + 1 < nb) issue_s(j + 1);
-        issue_pv(j);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          if (j < nb_t[t] && ok) issue_pv(t, j);
+          if (j + 1 < nb_t[t] && ok) issue_s(t, j + 1);
+        }
+        if (ok) tc_commit(&kv_empty[j % ST]);
       }
     }
+  }
   } else {
-    const int quad = warp & 3;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int t = (warp - 4) >> 2;                          // the tile this warpgroup serves
+    const int quad = warp & 3;                              // the 32 TMEM lanes this warp may touch
     const int row = quad * 32 + lane;                       // tile row = TMEM lane
-    const int rows_used = t_count * p.group;
+    const int my_nb = nb_t[t];
+    const int rows_used = max(t_count[t], 0) * p.group;
     const bool valid = row < rows_used;
-    const int pos = valid ? pos_first + row / p.group : -1;
+    const int pos_first = before + t_first[t];
+    // rows past the tile's tokens compute like its last row and are never stored
+    const int pos = pos_first + (valid ? row / p.group : max(t_count[t] - 1, 0));
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + C::S_COL + t * KB, o_addr = lane_addr + C::O_COL + t * HD;
     const float c_log2 = p.scale_log2;
-    float o_reg[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o_reg[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    // every lane of a warp must take the same path around the warp-wide TMEM loads, also when a
+    // every lane of a warp must take the same path around the warp-wide TMEM accesses, also when a
     // wait gives up
     auto wait_all = [&](uint64_t* bar, uint32_t parity) {       // one lane waits, the warp follows
       int done = lane == 0 ? (int)mbar_wait(bar, parity, &abort_flag) : 0;
       return __shfl_sync(0xffffffffu, done, 0) != 0;
     };
-    auto accumulate = [&](int j, float alpha) {            // o = o * alpha + O_j
-      const int sb = j % NBUF;
-      ok = ok && wait_all(&o_full[sb], (j / NBUF) & 1u);
-      tc_fence_after();
-      if (!ok) return;
-#pragma unroll
-      for (int ch = 0; ch < HD / 32; ++ch) {
-        uint32_t v[32];
-        tc_ld32(lane_addr + O_COL + sb * HD + ch * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_reg[ch * 32 + i] = fmaf(o_reg[ch * 32 + i], alpha, __uint_as_float(v[i]));
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_empty[sb]);
-    };
 
-    for (int j = 0; j < nb && ok; ++j) {
-      const int sb = j % NBUF;
+    for (int j = 0; j < my_nb && ok; ++j) {
       const int key0 = (b_lo + j) * KB;
-      ok = wait_all(&s_full[sb], (j / NBUF) & 1u);
+      ok = wait_all(&s_full[t], j & 1u);
       tc_fence_after();
       if (!ok) break;
+      float v[KB];
+#pragma unroll
+      for (int ch = 0; ch < KB / 32; ++ch) tc_ld32(s_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[ch * 32]));
+      tc_wait_ld();
       // keys this row may see: [key_min, pos]; blocks wholly inside need no per-element test
       const int key_min = p.window > 0 ? pos - p.window + 1 : -(1 << 30);
-      const bool need_mask = key0 + KB - 1 > pos || key0 < key_min;
-      // pass 1: row maximum (four independent chains)
+      const bool need_mask = __any_sync(0xffffffffu, key0 + KB - 1 > pos || key0 < key_min);
+      if (need_mask) {
+        const int hi = pos - key0, lo = key_min - key0;
+#pragma unroll
+        for (int i = 0; i < KB; ++i) v[i] = (i <= hi && i >= lo) ? v[i] : -INFINITY;
+      }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-      for (int ch = 0; ch < KB / 32; ++ch) {
-        uint32_t v[32];
-        tc_ld32(lane_addr + S_COL + sb * KB + ch * 32, v);
-        tc_wait_ld();
-        if (need_mask) {
-          const int kb = key0 + ch * 32;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool seen = kb + i <= pos && kb + i >= key_min;
-            mx[i & 3] = fmaxf(mx[i & 3], seen ? __uint_as_float(v[i]) : -INFINITY);
+      for (int i = 0; i < KB; i += 8) {
+        mx[0] = max3(mx[0], v[i], v[i + 1]);
+        mx[1] = max3(mx[1], v[i + 2], v[i + 3]);
+        mx[2] = max3(mx[2], v[i + 4], v[i + 5]);
+        mx[3] = max3(mx[3], v[i + 6], v[i + 7]);
+      }
+      const float m_new = fmaxf(max3(mx[0], mx[1], mx[2]), fmaxf(mx[3], m_run));
+      // move the maximum only when it grew by more than 2^RESCALE_LOG2 (always from -inf)
+      const bool grow = (m_new - m_run) * c_log2 > RESCALE_LOG2;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = fast_exp2((m_run - m_use) * c_log2);       // 0 from -inf
+        m_run = m_new;
+        l_run *= alpha;
+        if (j > 0) {                                   // O_t holds the blocks before this one: rescale its rows
+          ok = wait_all(&o_done[t], (j - 1) & 1u);
+          tc_fence_after();
+          if (!ok) break;
+#pragma unroll
+          for (int ch = 0; ch < HD / 32; ++ch) {
+            uint32_t o[32];
+            tc_ld32(o_addr + ch * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc_st32(o_addr + ch * 32, o);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
         }
       }
-      const float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_run);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2((m_run - m_use) * c_log2);
-      const float neg_mc = -m_use * c_log2;
-      m_run = m_new;
-      // the P buffer is free once the MMA that read it has completed
-      ok = wait_all(&p_empty[sb], ((j / NBUF) & 1u) ^ 1u);
-      if (!ok) break;
-      // pass 2: exponentials -> bf16 P row in the 128-byte swizzle: 16-byte chunk c of row r sits
-      // at chunk position c ^ (r % 8) of its 128-byte line
+      const float neg_mc = m_run == -INFINITY ? 0.f : -m_run * c_log2;
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* p_row = p_s + sb * P_BYTES + row * 128;
-#pragma unroll 1
-      for (int ch = 0; ch < KB / 32; ++ch) {
-        uint32_t v[32];
-        tc_ld32(lane_addr + S_COL + sb * KB + ch * 32, v);
-        tc_wait_ld();
-        float e[32];
-        if (need_mask) {
-          const int kb = key0 + ch * 32;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool seen = kb + i <= pos && kb + i >= key_min;
-            e[i] = seen ? fast_exp2(fmaf(__uint_as_float(v[i]), c_log2, neg_mc)) : 0.f;
-          }
-        } else {
+      for (int ch = 0; ch < KB / 64; ++ch) {             // 64 keys = 32 columns of packed bf16 per store
+        uint32_t packed[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(v[i]), c_log2, neg_mc));
-        }
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          ls[(i >> 1) & 3] += e[i] + e[i + 1];
-          __nv_bfloat162 b = __floats2bfloat162_rn(e[i], e[i + 1]);
+        for (int i = 0; i < 64; i += 2) {
+          const float e0 = fast_exp2(fmaf(v[ch * 64 + i], c_log2, neg_mc));
+          const float e1 = fast_exp2(fmaf(v[ch * 64 + i + 1], c_log2, neg_mc));
+          ls[(i >> 1) & 3] += e0 + e1;
+          __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
           packed[i / 2] = *reinterpret_cast<uint32_t*>(&b);
         }
-        unsigned char* slab = p_row + (ch / 2) * (P_BYTES / 2);           // keys 0-63 | 64-127
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {                                   // four 16-byte chunks = 32 keys
-          const int chunk = (ch % 2) * 4 + q4;
-          *reinterpret_cast<uint4*>(slab + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-        }
+        tc_st32(s_addr + ch * 32, packed);
       }
-      const float l_add = (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      l_run = l_run * alpha + l_add;
-      // S buffer read completely; P written: make it visible to the tensor core's (async) reads
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // P (and a rescaled O) must have landed in tensor memory before the MMA is told
+      tc_wait_st();
       tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full[sb]); }
-      // fold in the previous block's output while the tensor core works on this one
-      if (j > 0) accumulate(j - 1, alpha_prev);
-      alpha_prev = alpha;
+      if (lane == 0) mbar_arrive(&p_full[t]);
     }
-    if (ok && nb > 0) accumulate(nb - 1, alpha_prev);
 
-    if (ok && valid) {
-      const int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
+    if (ok && my_nb > 0) {
+      ok = wait_all(&o_done[t], (my_nb - 1) & 1u);
+      tc_fence_after();
+    }
+    if (ok && my_nb > 0) {
+      const int tk = t_first[t] + row / p.group, head = kvh * p.group + row % p.group;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
+      __nv_bfloat16* dst = p.out + (long long)(tok0 + tk) * p.ld_o + (long long)head * HD;
 #pragma unroll
-      for (int d = 0; d < HD; d += 8) {
-        uint4 o;
-        __nv_bfloat162 b0 = __floats2bfloat162_rn(o_reg[d] * inv, o_reg[d + 1] * inv);
-        __nv_bfloat162 b1 = __floats2bfloat162_rn(o_reg[d + 2] * inv, o_reg[d + 3] * inv);
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(o_reg[d + 4] * inv, o_reg[d + 5] * inv);
-        __nv_bfloat162 b3 = __floats2bfloat162_rn(o_reg[d + 6] * inv, o_reg[d + 7] * inv);
-        o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
-        o.z = *reinterpret_cast<uint32_t*>(&b2); o.w = *reinterpret_cast<uint32_t*>(&b3);
-        *reinterpret_cast<uint4*>(dst + d) = o;
+      for (int ch = 0; ch < HD / 32; ++ch) {
+        uint32_t o[32];
+        tc_ld32(o_addr + ch * 32, o);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int d = 0; d < 32; d += 8) {
+            uint4 w;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + 4]) * inv, __uint_as_float(o[d + 5]) * inv);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(o[d + 6]) * inv, __uint_as_float(o[d + 7]) * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&b0); w.y = *reinterpret_cast<uint32_t*>(&b1);
+            w.z = *reinterpret_cast<uint32_t*>(&b2); w.w = *reinterpret_cast<uint32_t*>(&b3);
+            *reinterpret_cast<uint4*>(dst + ch * 32 + d) = w;
+          }
+        }
       }
     }
   }
@@ -347,7 +439,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
   }
 }
 
@@ -364,11 +456,28 @@ int make_map_4d(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4],
   return HFEE_OK;
 }
 
+template <int HD, int NT>
+int launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, TcAttnParams p, int kv_heads,
+              int requests, int* status, cudaStream_t stream) {
+  using C = TcCfg<HD, NT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<HD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess)
+      return hfee_fail(HFEE_ERR_CUDA, "attention_tc: cannot get %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  p.q_groups = (p.q_tiles + NT - 1) / NT;
+  dim3 grid((unsigned)kv_heads, (unsigned)p.q_groups, (unsigned)requests);
+  hfee_launch(attention_tc_kernel<HD, NT>, grid, dim3(C::THREADS), C::SMEM, stream, mq, mk, mv, p, status);
+  return hfee_check_launch("attention_tc");
+}
+
 }  // namespace
 
 // 1 if hfee_attention_tc takes this shape (bfloat16 is implied).
 HFEE_API int hfee_attention_tc_supports(int heads, int kv_heads, int head_dim, int page_size) {
-  if (head_dim != HD || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+  if ((head_dim != 64 && head_dim != 128) || kv_heads <= 0 || heads % kv_heads != 0) return 0;
   int group = heads / kv_heads;
   if (group > QM) return 0;
   if (page_size < 64 || (page_size & (page_size - 1)) != 0) return 0;
@@ -383,8 +492,8 @@ HFEE_API int hfee_attention_tc(const void* q, int ld_q, const void* k_pool, cons
                                int window, int* status, cudaStream_t stream) {
   if (n_tokens == 0 || requests == 0) return HFEE_OK;
   HFEE_REQUIRE(hfee_attention_tc_supports(heads, kv_heads, head_dim, page_size),
-               "attention_tc: needs head_dim 64, at most 128 query heads per kv head and power-of-two pages >= 64 "
-               "(got head_dim %d, heads %d/%d, page_size %d)", head_dim, heads, kv_heads, page_size);
+               "attention_tc: needs head_dim 64 or 128, at most 128 query heads per kv head and power-of-two pages "
+               ">= 64 (got head_dim %d, heads %d/%d, page_size %d)", head_dim, heads, kv_heads, page_size);
   HFEE_REQUIRE(ld_q % 8 == 0 && ld_o % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0,
                "attention_tc: q and out must be 16-byte aligned with leading dimensions %% 8 == 0");
   HFEE_REQUIRE(requests <= 65535 && max_new > 0 && max_new / (QM / (heads / kv_heads)) < 65535 && num_pages > 0,
@@ -401,33 +510,27 @@ HFEE_API int hfee_attention_tc(const void* q, int ld_q, const void* k_pool, cons
   p.window = window;
   p.tokens_per_tile = QM / group;
   p.q_tiles = (max_new + p.tokens_per_tile - 1) / p.tokens_per_tile;
+  p.q_groups = 0;
 
   CUtensorMap mq, mk, mv;
   {
-    // q as [token][kv head][head of group][d]; a tile is (tokens_per_tile x group) rows of 64 d
-    const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)group, (cuuint64_t)kv_heads, (cuuint64_t)n_tokens};
-    const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)group * HD * 2, (cuuint64_t)ld_q * 2};
-    const cuuint32_t box[4] = {(cuuint32_t)HD, (cuuint32_t)group, 1, (cuuint32_t)p.tokens_per_tile};
+    // q as [token][kv head][head of group][d]; a box is (tokens_per_tile x group) rows of 64 d
+    const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)group, (cuuint64_t)kv_heads, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)group * head_dim * 2, (cuuint64_t)ld_q * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)group, 1, (cuuint32_t)p.tokens_per_tile};
     int rc = make_map_4d(&mq, q, dims, strides, box);
     if (rc != HFEE_OK) return rc;
   }
   {
-    const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)num_pages};
-    const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)page_size * HD * 2,
-                                   (cuuint64_t)kv_heads * page_size * HD * 2};
-    const cuuint32_t box[4] = {(cuuint32_t)HD, 64, 1, 1};
+    const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2,
+                                   (cuuint64_t)kv_heads * page_size * head_dim * 2};
+    const cuuint32_t box[4] = {64, 64, 1, 1};
     int rc = make_map_4d(&mk, k_pool, dims, strides, box);
     if (rc != HFEE_OK) return rc;
     rc = make_map_4d(&mv, v_pool, dims, strides, box);
     if (rc != HFEE_OK) return rc;
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
-    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_tc: cannot get %d bytes of shared memory: %s", AT_SMEM, cudaGetErrorString(e));
-    configured = true;
-  }
-  dim3 grid((unsigned)kv_heads, (unsigned)p.q_tiles, (unsigned)requests);
-  hfee_launch(attention_tc_kernel, grid, dim3(AT_THREADS), AT_SMEM, stream, mq, mk, mv, p, status);
-  return hfee_check_launch("attention_tc");
+  if (head_dim == 64) return launch_tc<64, 2>(mq, mk, mv, p, kv_heads, requests, status, stream);
+  return launch_tc<128, 2>(mq, mk, mv, p, kv_heads, requests, status, stream);
 }

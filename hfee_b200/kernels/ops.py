@@ -493,8 +493,8 @@ USE_TC_ATTENTION = True
 
 def attention_tc(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, context_before, out, n_tokens,
                  requests, max_new, heads, kv_heads, head_dim, scale, window=0) -> None:
-    """Flash attention for prompt portions on tcgen05 (S and O accumulators in tensor memory, TMA-fed
-    pages, one softmax thread per query row).  bfloat16, head size 64, pages of at least 64 tokens."""
+    """Flash attention for prompt portions on tcgen05 (S, P and O in tensor memory, TMA-fed pages, one
+    softmax thread per query row).  bfloat16, head size 64 or 128, pages of at least 64 tokens."""
     lib = library()
     for t, what in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (slots, "slots"),
                     (context_before, "context_before")):
