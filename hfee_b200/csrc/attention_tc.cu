@@ -45,9 +45,15 @@ struct TcCfg {
   static constexpr int TILE_BYTES = NT * Q_BYTES + STAGES * 2 * KT_BYTES;
   static constexpr int SMEM = TILE_BYTES + 256;            // + barriers; the base must come 1024-aligned (checked)
   static constexpr int THREADS = 128 + NT * 128;      // warpgroup 0: producer and MMA warps; one warpgroup per tile
-  static constexpr uint32_t S_COL = 0, O_COL = NT * KB;    // S_t at t*128, O_t at O_COL + t*HD
-  static constexpr uint32_t TMEM_COLS = NT * (KB + HD) <= 256 ? 256 : 512;
-  static constexpr int N_BARS = NT + 3 * STAGES + 3 * NT + 1;
+  // Tensor memory: S_t at t*128.  When the 512 columns allow it (head size 64) P_t has 64 columns of
+  // its own, so that S_t is free again as soon as the softmax threads hold it in registers and the
+  // next S_t is computed while they work; else P_t overwrites the first half of S_t.  O_t behind them.
+  static constexpr bool SEP_P = NT * (KB + KB / 2 + HD) <= 512;
+  static constexpr uint32_t S_COL = 0, P_COL = SEP_P ? NT * KB : 0, P_STRIDE = SEP_P ? KB / 2 : KB;
+  static constexpr uint32_t O_COL = SEP_P ? NT * (KB + KB / 2) : NT * KB;      // O_t at O_COL + t*HD
+  static constexpr uint32_t TMEM_COLS = O_COL + NT * HD <= 256 ? 256 : 512;
+  static_assert(O_COL + NT * HD <= 512, "tensor memory");
+  static constexpr int N_BARS = NT + 3 * STAGES + 5 * NT + 1;
   static_assert(N_BARS * 8 + 8 <= 256, "barrier area");
   static_assert(SMEM <= 227 * 1024, "shared memory");
 };
@@ -108,6 +114,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two float32 operations in one instruction.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)), "l"(reinterpret_cast<uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+  return d;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -131,7 +152,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* s_full = kv_empty + ST;        // [NT]  S_t of the current block is in tensor memory
   uint64_t* p_full = s_full + NT;          // [NT]  P_t is in tensor memory (and O_t rescaled if it had to be)
   uint64_t* o_done = p_full + NT;          // [NT]  the MMAs O_t += P_t V of the current block have completed
-  uint64_t* v_clean = o_done + NT;         //       the last block's V rows behind the last position are cleared
+  uint64_t* s_free = o_done + NT;          // [NT]  the softmax threads hold S_t in registers (SEP_P only)
+  uint64_t* turn = s_free + NT;            // [NT]  tile t's softmax threads may compute their exponentials (SEP_P only)
+  uint64_t* v_clean = turn + NT;           //       the last block's V rows behind the last position are cleared
   uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(v_clean + 1);
   int& abort_flag = *reinterpret_cast<int*>(reinterpret_cast<uint32_t*>(v_clean + 1) + 1);
   unsigned char* q_s = base;                                  // [NT][slab][128 rows][64]
@@ -168,7 +191,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     abort_flag = (smem_u32(base) & 1023u) != 0 ? 1 : 0;       // misaligned tiles would corrupt the swizzle
     for (int t = 0; t < NT; ++t) {
       mbar_init(&q_full[t], 1);
-      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1);
+      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); mbar_init(&s_free[t], 4); mbar_init(&turn[t], 4);
     }
     for (int s = 0; s < ST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(v_clean, 1);
@@ -184,93 +207,105 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();                       // queries and this step's keys/values come from the previous kernels
   pdl_launch_dependents();
-  // the softmax threads hold a whole row of S: they take the registers the first warpgroup does not need
+  // The softmax threads hold a whole row of S: they take registers the first warpgroup does not need.
+  // The kernel starts with 168 registers per thread (65,536 / 384 rounded down to a multiple of 8);
+  // setmaxnreg.inc waits until the CTA's pool holds what it asks for, so what the first warpgroup
+  // gives up (168 - 64 each) must cover what the others take (216 - 168 each) or the CTA hangs.
+  static_assert(128 * (168 - 64) >= NT * 128 * (216 - 168), "register hand-over");
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 0) {
-    if (lane == 0) {
-      // a query box is tokens_per_tile x group rows (fewer than 128 when the group does not divide
-      // 128; the rows left over are never read back), 64 head dims per load
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 0) {
+      if (lane == 0) {
+        // a query box is tokens_per_tile x group rows (fewer than 128 when the group does not divide
+        // 128; the rows left over are never read back), 64 head dims per load
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        if (nb_t[t] == 0) continue;
-        mbar_expect_tx(&q_full[t], (uint32_t)(p.tokens_per_tile * p.group * HD * 2));
-#pragma unroll
-        for (int h = 0; h < C::SLABS; ++h)
-          tma_load_4d(q_s + t * C::Q_BYTES + h * SLAB_BYTES, &map_q, h * 64, 0, kvh, tok0 + t_first[t], &q_full[t]);
-      }
-      bool ok = true;
-      for (int j = 0; j < nb && ok; ++j) {
-        const int s = j % ST;
-        ok = mbar_wait(&kv_empty[s], ((j / ST) & 1u) ^ 1u, &abort_flag);
-        if (!ok) break;
-        int page[2], in_page[2];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {                       // two pieces of 64 keys
-          const int key0 = (b_lo + j) * KB + c * 64;
-          // a piece beyond the pages the request holds reads page -1: out of range, zero-filled
-          page[c] = (key0 >> p.page_shift) < p.max_pages
-                        ? p.block_table[(long long)slot * p.max_pages + (key0 >> p.page_shift)] : -1;
-          in_page[c] = key0 & (p.page_size - 1);
-        }
-        unsigned char* k_dst = kv_s + s * 2 * C::KT_BYTES;
-        mbar_expect_tx(&k_full[s], C::KT_BYTES);
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int t = 0; t < NT; ++t) {
+          if (nb_t[t] == 0) continue;
+          mbar_expect_tx(&q_full[t], (uint32_t)(p.tokens_per_tile * p.group * HD * 2));
 #pragma unroll
           for (int h = 0; h < C::SLABS; ++h)
-            tma_load_4d(k_dst + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_k, h * 64, in_page[c], kvh, page[c], &k_full[s]);
-        mbar_expect_tx(&v_full[s], C::KT_BYTES);
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int h = 0; h < C::SLABS; ++h)
-            tma_load_4d(k_dst + C::KT_BYTES + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_v, h * 64, in_page[c], kvh,
-                        page[c], &v_full[s]);
-      }
-    }
-    __syncwarp();
-    // The last block's V rows of positions behind the CTA's last token: their P is zero, but a page
-    // that another request used before may hold anything there, and 0 * NaN is NaN.  Clear them.
-    if (nb > 0) {
-      const int j = nb - 1, s = j % ST;
-      int done = lane == 0 ? (int)mbar_wait(&v_full[s], (j / ST) & 1u, &abort_flag) : 0;
-      done = __shfl_sync(0xffffffffu, done, 0);
-      const int first_row = pos_last_all - (b_lo + j) * KB + 1;       // 1..128
-      if (done && first_row < KB) {
-        unsigned char* v_dst = kv_s + s * 2 * C::KT_BYTES + C::KT_BYTES;
-        const int per_slab = (KB - first_row) * 8;                    // 16-byte pieces
-        for (int i = lane; i < per_slab * C::SLABS; i += 32) {
-          const int h = i / per_slab, o = i % per_slab;
-          *reinterpret_cast<uint4*>(v_dst + h * SLAB_BYTES + first_row * 128 + o * 16) = make_uint4(0, 0, 0, 0);
+            tma_load_4d(q_s + t * C::Q_BYTES + h * SLAB_BYTES, &map_q, h * 64, 0, kvh, tok0 + t_first[t], &q_full[t]);
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        bool ok = true;
+#pragma unroll 1
+        for (int j = 0; j < nb && ok; ++j) {
+          const int s = j % ST;
+          ok = mbar_wait(&kv_empty[s], ((j / ST) & 1u) ^ 1u, &abort_flag);
+          if (!ok) break;
+          int page[2], in_page[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {                       // two pieces of 64 keys
+            const int key0 = (b_lo + j) * KB + c * 64;
+            // a piece beyond the pages the request holds reads page -1: out of range, zero-filled
+            page[c] = (key0 >> p.page_shift) < p.max_pages
+                          ? p.block_table[(long long)slot * p.max_pages + (key0 >> p.page_shift)] : -1;
+            in_page[c] = key0 & (p.page_size - 1);
+          }
+          unsigned char* k_dst = kv_s + s * 2 * C::KT_BYTES;
+          mbar_expect_tx(&k_full[s], C::KT_BYTES);
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int h = 0; h < C::SLABS; ++h)
+              tma_load_4d(k_dst + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_k, h * 64, in_page[c], kvh, page[c], &k_full[s]);
+          mbar_expect_tx(&v_full[s], C::KT_BYTES);
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int h = 0; h < C::SLABS; ++h)
+              tma_load_4d(k_dst + C::KT_BYTES + h * SLAB_BYTES + c * (SLAB_BYTES / 2), &map_v, h * 64, in_page[c], kvh,
+                          page[c], &v_full[s]);
+        }
       }
       __syncwarp();
-      if (lane == 0 && done) mbar_arrive(v_clean);
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
+      // The last block's V rows of positions behind the CTA's last token: their P is zero, but a page
+      // that another request used before may hold anything there, and 0 * NaN is NaN.  Clear them.
+      if (nb > 0) {
+        const int j = nb - 1, s = j % ST;
+        int done = lane == 0 ? (int)mbar_wait(&v_full[s], (j / ST) & 1u, &abort_flag) : 0;
+        done = __shfl_sync(0xffffffffu, done, 0);
+        const int first_row = pos_last_all - (b_lo + j) * KB + 1;       // 1..128
+        if (done && first_row < KB) {
+          unsigned char* v_dst = kv_s + s * 2 * C::KT_BYTES + C::KT_BYTES;
+          const int per_slab = (KB - first_row) * 8;                    // 16-byte pieces
+          for (int i = lane; i < per_slab * C::SLABS; i += 32) {
+            const int h = i / per_slab, o = i % per_slab;
+            *reinterpret_cast<uint4*>(v_dst + h * SLAB_BYTES + first_row * 128 + o * 16) = make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 0 && done) mbar_arrive(v_clean);
+      }
+    } else if (warp == 1) {
+      // The whole warp walks the loop (so that control flow stays warp-uniform and addresses and
+      // descriptors can live in uniform registers); one elected lane issues the MMAs and commits.
       constexpr uint32_t idesc_s = make_idesc(QM, KB);                       // A, B K-major
       constexpr uint32_t idesc_o = make_idesc(QM, 64) | (1u << 16);          // B (V) MN-major, 64 head dims per MMA
       bool ok = true;
       auto wait = [&](uint64_t* bar, uint32_t parity) {
-        ok = ok && mbar_wait(bar, parity, &abort_flag);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, &abort_flag));
         return ok;
       };
+      const uint64_t q_desc = make_desc(smem_u32(q_s)), kv_desc = make_desc(smem_u32(kv_s));
+      const uint64_t v_desc = make_desc_mn(smem_u32(kv_s) + C::KT_BYTES, 16, 1024);
       auto issue_s = [&](int t, int j) {
         const int s = j % ST;
         if (!wait(&k_full[s], (j / ST) & 1u)) return;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(q_s + t * C::Q_BYTES), k_addr = smem_u32(kv_s + s * 2 * C::KT_BYTES);
+        if (elect_one()) {
+          // descriptor addresses count 16-byte units
+          const uint64_t dq = q_desc + (uint64_t)(t * (C::Q_BYTES >> 4)), dk = kv_desc + (uint64_t)(s * (2 * C::KT_BYTES >> 4));
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks / 4) * SLAB_BYTES;          // 16 head dims = 32 bytes further along a slab's rows
-          tc_mma(tmem_base + C::S_COL + t * KB, make_desc(q_addr + off) + 2 * (ks % 4),
-                 make_desc(k_addr + off) + 2 * (ks % 4), idesc_s, ks != 0);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            // 16 head dims = 32 bytes further along a slab's rows; the next slab after four of them
+            const uint32_t off = (ks / 4) * (SLAB_BYTES >> 4) + 2 * (ks % 4);
+            tc_mma(tmem_base + C::S_COL + t * KB, dq + off, dk + off, idesc_s, ks != 0);
+          }
+          tc_commit(&s_full[t]);
         }
-        tc_commit(&s_full[t]);
+        __syncwarp();
       };
       auto issue_pv = [&](int t, int j) {
         const int s = j % ST;
@@ -278,16 +313,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!wait(&v_full[s], (j / ST) & 1u)) return;
         if (j == nb - 1 && !wait(v_clean, 0)) return;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(kv_s + s * 2 * C::KT_BYTES + C::KT_BYTES);
+        if (elect_one()) {
+          const uint64_t dv = v_desc + (uint64_t)(s * (2 * C::KT_BYTES >> 4));
+          const uint32_t acc = j > 0 ? 1u : 0u;
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; ++kk) {
-          // P: 16 keys = 8 columns of packed bf16 further; V: 16 keys = two 8-row groups of 1024 bytes
+          for (int kk = 0; kk < KB / 16; ++kk) {
+            // P: 16 keys = 8 columns of packed bf16 further; V: 16 keys = two 8-row groups of 1024 bytes
 #pragma unroll
-          for (int h = 0; h < C::SLABS; ++h)
-            tc_mma_ts(tmem_base + C::O_COL + t * HD + h * 64, tmem_base + C::S_COL + t * KB + kk * 8,
-                      make_desc_mn(v_addr + h * SLAB_BYTES + kk * 2048, 16, 1024), idesc_o, (j > 0 || kk != 0) ? 1u : 0u);
+            for (int h = 0; h < C::SLABS; ++h)
+              tc_mma_ts(tmem_base + C::O_COL + t * HD + h * 64, tmem_base + C::P_COL + t * C::P_STRIDE + kk * 8,
+                        dv + (uint64_t)(h * (SLAB_BYTES >> 4) + kk * (2048 >> 4)), idesc_o, kk != 0 ? 1u : acc);
+          }
+          tc_commit(&o_done[t]);
         }
-        tc_commit(&o_done[t]);
+        __syncwarp();
       };
 #pragma unroll
       for (int t = 0; t < NT; ++t)
@@ -295,18 +334,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int t = 0; t < NT; ++t)
         if (nb_t[t] > 0 && ok) issue_s(t, 0);
+#pragma unroll 1
       for (int j = 0; j < nb && ok; ++j) {
+        if (C::SEP_P) {
+          // the next S_t as soon as the softmax threads have taken this one out of tensor memory
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (j < nb_t[t] && ok) issue_pv(t, j);
-          if (j + 1 < nb_t[t] && ok) issue_s(t, j + 1);
+          for (int t = 0; t < NT; ++t)
+            if (j + 1 < nb_t[t] && wait(&s_free[t], j & 1u)) issue_s(t, j + 1);
+#pragma unroll
+          for (int t = 0; t < NT; ++t)
+            if (j < nb_t[t] && ok) issue_pv(t, j);
+        } else {
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            if (j < nb_t[t] && ok) issue_pv(t, j);
+            if (j + 1 < nb_t[t] && ok) issue_s(t, j + 1);
+          }
         }
-        if (ok) tc_commit(&kv_empty[j % ST]);
+        if (ok && elect_one()) tc_commit(&kv_empty[j % ST]);
+        __syncwarp();
       }
     }
-  }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int t = (warp - 4) >> 2;                          // the tile this warpgroup serves
     const int quad = warp & 3;                              // the 32 TMEM lanes this warp may touch
     const int row = quad * 32 + lane;                       // tile row = TMEM lane
@@ -318,17 +368,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int pos = pos_first + (valid ? row / p.group : max(t_count[t] - 1, 0));
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t s_addr = lane_addr + C::S_COL + t * KB, o_addr = lane_addr + C::O_COL + t * HD;
+    const uint32_t p_addr = lane_addr + C::P_COL + t * C::P_STRIDE;
     const float c_log2 = p.scale_log2;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    // With S_t ready ahead of time the two tiles' softmax threads would run in step and meet in the
+    // special-function unit while the other pipes idle, then leave it idle together.  Tile 1 starts
+    // its first exponentials when tile 0 has finished its own, which puts the two half a block apart:
+    // one tile's exponentials then run beside the other's loads, maxima and waits.
+    const int nb_turns = (C::SEP_P && NT == 2) ? min(1, min(nb_t[0], nb_t[NT - 1])) : 0;
+    if (t == 1 && nb_turns > 0) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&turn[0]);                // tile 0 begins
+    }
 
     // every lane of a warp must take the same path around the warp-wide TMEM accesses, also when a
     // wait gives up
-    auto wait_all = [&](uint64_t* bar, uint32_t parity) {       // one lane waits, the warp follows
-      int done = lane == 0 ? (int)mbar_wait(bar, parity, &abort_flag) : 0;
-      return __shfl_sync(0xffffffffu, done, 0) != 0;
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {       // no lane goes on alone
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, &abort_flag)) != 0;
     };
 
+#pragma unroll 1
     for (int j = 0; j < my_nb && ok; ++j) {
       const int key0 = (b_lo + j) * KB;
       ok = wait_all(&s_full[t], j & 1u);
@@ -338,6 +398,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int ch = 0; ch < KB / 32; ++ch) tc_ld32(s_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[ch * 32]));
       tc_wait_ld();
+      if (C::SEP_P) {                      // S_t is in registers: the MMA warp may compute the next one
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[t]);
+      }
       // keys this row may see: [key_min, pos]; blocks wholly inside need no per-element test
       const int key_min = p.window > 0 ? pos - p.window + 1 : -(1 << 30);
       const bool need_mask = __any_sync(0xffffffffu, key0 + KB - 1 > pos || key0 < key_min);
@@ -357,6 +422,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const float m_new = fmaxf(max3(mx[0], mx[1], mx[2]), fmaxf(mx[3], m_run));
       // move the maximum only when it grew by more than 2^RESCALE_LOG2 (always from -inf)
       const bool grow = (m_new - m_run) * c_log2 > RESCALE_LOG2;
+      bool o_waited = false;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
         const float alpha = fast_exp2((m_run - m_use) * c_log2);       // 0 from -inf
@@ -366,6 +432,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           ok = wait_all(&o_done[t], (j - 1) & 1u);
           tc_fence_after();
           if (!ok) break;
+          o_waited = true;
 #pragma unroll
           for (int ch = 0; ch < HD / 32; ++ch) {
             uint32_t o[32];
@@ -377,22 +444,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
         }
       }
+      if (C::SEP_P && j > 0 && !o_waited) {            // the MMA that read the last P_t must be through with it
+        ok = wait_all(&o_done[t], (j - 1) & 1u);
+        tc_fence_after();
+        if (!ok) break;
+      }
+      if (j < nb_turns) {
+        ok = wait_all(&turn[t], j & 1u);
+        if (!ok) break;
+      }
       const float neg_mc = m_run == -INFINITY ? 0.f : -m_run * c_log2;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const float2 c2 = make_float2(c_log2, c_log2), n2 = make_float2(neg_mc, neg_mc);
+      float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int ch = 0; ch < KB / 64; ++ch) {             // 64 keys = 32 columns of packed bf16 per store
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
-          const float e0 = fast_exp2(fmaf(v[ch * 64 + i], c_log2, neg_mc));
-          const float e1 = fast_exp2(fmaf(v[ch * 64 + i + 1], c_log2, neg_mc));
-          ls[(i >> 1) & 3] += e0 + e1;
-          __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+          const float2 x = fma2(make_float2(v[ch * 64 + i], v[ch * 64 + i + 1]), c2, n2);
+          const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          ls[(i >> 1) & 1] = add2(ls[(i >> 1) & 1], e);
+          __nv_bfloat162 b = __floats2bfloat162_rn(e.x, e.y);
           packed[i / 2] = *reinterpret_cast<uint32_t*>(&b);
         }
-        tc_st32(s_addr + ch * 32, packed);
+        tc_st32(p_addr + ch * 32, packed);
       }
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      l_run += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
+      if (j < nb_turns) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&turn[NT - 1 - t]);
+      }
       // P (and a rescaled O) must have landed in tensor memory before the MMA is told
       tc_wait_st();
       tc_fence_before();
@@ -433,6 +514,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (abort_flag) {
+#pragma unroll 1
     for (int i = 0; i < 400; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 2);
     __syncthreads();

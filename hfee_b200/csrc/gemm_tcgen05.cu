@@ -123,51 +123,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   pdl_launch_dependents();
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;                           // K blocks issued so far, over all segments
-      bool ok = true;
-      Walk w = walk_start();
-      int t, kb0, kb1;
-      while (ok && walk_next(w, t, kb0, kb1)) {
-        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag);
-          if (!ok) break;
+    // Producer and MMA warps walk their loops as whole warps: control flow stays warp-uniform, so
+    // addresses and descriptors can be kept in uniform registers, and one elected lane issues.
+    uint32_t it = 0;                           // K blocks issued so far, over all segments
+    bool ok = true;
+    Walk w = walk_start();
+    int t, kb0, kb1;
+    while (ok && walk_next(w, t, kb0, kb1)) {
+      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % STAGES;
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag));
+        if (!ok) break;
+        if (elect_one()) {
           unsigned char* a_dst = tiles + s * Cfg::STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, kb * BK, m0, &full_bar[s]);
           tma_load_2d(a_dst + Cfg::A_BYTES, &map_w, kb * BK, n0, &full_bar[s]);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
-      uint32_t it = 0, acc_it = 0;
-      bool ok = true;
-      Walk w = walk_start();
-      int t, kb0, kb1;
-      for (; ok && walk_next(w, t, kb0, kb1); ++acc_it) {
-        const uint32_t buf = acc_it & 1u;
-        ok = mbar_wait(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, &abort_flag);   // epilogue has drained it
+    constexpr uint32_t idesc = make_idesc(BM, BN);
+    uint32_t it = 0, acc_it = 0;
+    bool ok = true;
+    Walk w = walk_start();
+    int t, kb0, kb1;
+    const uint64_t desc0 = make_desc(smem_u32(tiles));
+    for (; ok && walk_next(w, t, kb0, kb1); ++acc_it) {
+      const uint32_t buf = acc_it & 1u;
+      // the epilogue has drained this accumulator
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, &abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % STAGES;
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / STAGES) & 1u, &abort_flag));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1u, &abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + s * Cfg::STAGE_BYTES);
-          const uint64_t da = make_desc(a_addr), dw = make_desc(a_addr + Cfg::A_BYTES);
+        if (elect_one()) {
+          // descriptor addresses count 16-byte units
+          const uint64_t da = desc0 + (uint64_t)(s * (Cfg::STAGE_BYTES >> 4)), dw = da + (uint64_t)(Cfg::A_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)       // 16 bf16 = 32 bytes further along K: +2 in 16-byte units
             tc_mma(tmem_d, da + 2 * k, dw + 2 * k, idesc, kb > kb0 || k != 0);
           tc_commit(&empty_bar[s]);
         }
-        if (ok) tc_commit(&tmem_full_bar[buf]);
+        __syncwarp();
       }
+      if (ok && elect_one()) tc_commit(&tmem_full_bar[buf]);
+      __syncwarp();
     }
   } else {
     // epilogue warp w may read TMEM lanes 32*(w%4) .. +31 (= tile rows of the same numbers); the
@@ -362,6 +369,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   if (abort_flag) {
     // loads that were issued may still be landing in this CTA's shared memory: give them time
+#pragma unroll 1
     for (int i = 0; i < 400; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
     __syncthreads();

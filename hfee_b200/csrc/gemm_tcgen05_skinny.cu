@@ -158,32 +158,37 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(WM, TN);
-      uint32_t it = 0, acc_it = 0;
-      bool ok = true;
-      for (int i = blockIdx.x; i < items && ok; i += gridDim.x, ++acc_it) {
-        const int split = i / a.w_tiles;
-        const int kb0 = split * a.kb_per_split, kb1 = min(a.k_blocks, kb0 + a.kb_per_split);
-        const uint32_t buf = acc_it & 1u;
-        ok = mbar_wait(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, &abort_flag);
+    // The whole warp walks the loop (warp-uniform control flow keeps addresses and descriptors in
+    // uniform registers); one elected lane issues the MMAs and commits.
+    constexpr uint32_t idesc = make_idesc(WM, TN);
+    uint32_t it = 0, acc_it = 0;
+    bool ok = true;
+    const uint64_t desc0 = make_desc(smem_u32(tiles));
+    for (int i = blockIdx.x; i < items && ok; i += gridDim.x, ++acc_it) {
+      const int split = i / a.w_tiles;
+      const int kb0 = split * a.kb_per_split, kb1 = min(a.k_blocks, kb0 + a.kb_per_split);
+      const uint32_t buf = acc_it & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, &abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * TN;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % STAGES;
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / STAGES) & 1u, &abort_flag));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * TN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1u, &abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t w_addr = smem_u32(tiles + s * Cfg::STAGE_BYTES);
-          const uint64_t dw = make_desc(w_addr), da = make_desc(w_addr + Cfg::W_BYTES);
+        if (elect_one()) {
+          // descriptor addresses count 16-byte units
+          const uint64_t dw = desc0 + (uint64_t)(s * (Cfg::STAGE_BYTES >> 4)), da = dw + (uint64_t)(Cfg::W_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             tc_mma(tmem_d, dw + 2 * k, da + 2 * k, idesc, (kb > kb0) || k != 0);
           tc_commit(&empty_bar[s]);
         }
-        if (ok) tc_commit(&tmem_full_bar[buf]);
+        __syncwarp();
       }
+      if (ok && elect_one()) tc_commit(&tmem_full_bar[buf]);
+      __syncwarp();
     }
   } else {
     pdl_wait();            // C (when accumulating) is the previous kernel's output
@@ -215,6 +220,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tc_fence_before();
   __syncthreads();
   if (abort_flag) {
+#pragma unroll 1
     for (int i = 0; i < 400; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
     __syncthreads();

@@ -10,7 +10,7 @@
 namespace tc {
 
 constexpr int BK = 64;                        // K elements per pipeline stage: one 128-byte swizzle row of bf16
-constexpr uint32_t WAIT_LIMIT = 1u << 18;     // suspended attempts before a wait gives up: about a second
+constexpr uint64_t WAIT_NS = 1000000000ull;   // a wait on a barrier gives up after a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -34,16 +34,48 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(8000u) : "memory");
   return ok != 0;
 }
-// Waits for the phase with `parity` to complete; false if the wait ran out (WAIT_LIMIT attempts of
-// at most a few microseconds each: about a second) or the CTA is aborting.  A suspended thread
-// issues no instructions, so waiting warps do not take issue slots from working ones.
+// Non-blocking test of the same.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with `parity` to complete; false if the wait ran out (WAIT_NS of wall time on
+// the GPU's nanosecond timer) or the CTA is aborting.  A suspended thread issues no instructions,
+// so waiting warps do not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  if (mbar_test(bar, parity)) return true;        // a phase that is already complete costs least this way
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+#pragma unroll 1
+  for (;;) {
     if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
+    if (global_ns() - t0 > WAIT_NS) break;
   }
   *abort_flag = 1;
   return false;
+}
+
+// True in exactly one lane of a converged warp.  Unlike a test of the lane id the compiler knows that
+// the branch leaves the warp's addresses and descriptors uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
