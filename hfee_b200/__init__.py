@@ -9,7 +9,7 @@ from .config import (ConfigError, EngineConfig, LayerSpec, LlamaConfig, ModelSpe
                      register_architecture)
 from .cache import CacheManager, FixedState, OutOfPages, PagedKV
 from .engine import Engine, GenerationResult, ModelRunner, Request, Scheduler, StepEntry
-from .parts import Mixer, Part, Runtime, register_part
+from .parts import Block, Mixer, Part, Runtime, register_part
 from .sampling import SamplingOptions
 from .weights import TensorNeed, WeightError, write_random_model
 
@@ -17,5 +17,5 @@ __version__ = "0.1.0"
 
 __all__ = ["ConfigError", "EngineConfig", "LayerSpec", "LlamaConfig", "ModelSpec", "PartSpec", "RunSpec",
            "register_architecture", "CacheManager", "FixedState", "OutOfPages", "PagedKV", "Engine",
-           "GenerationResult", "ModelRunner", "Request", "Scheduler", "StepEntry", "Mixer", "Part", "Runtime",
+           "GenerationResult", "ModelRunner", "Request", "Scheduler", "StepEntry", "Block", "Mixer", "Part", "Runtime",
            "register_part", "SamplingOptions", "TensorNeed", "WeightError", "write_random_model", "__version__"]

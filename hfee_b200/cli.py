@@ -45,20 +45,15 @@ def _rate(n: int, seconds: float) -> str:
 
 def _generate_once(engine, prompt, opts, verbose: bool, load_seconds: float, as_ids: bool) -> List[int]:
     t0 = time.perf_counter()
-    pieces: List[int] = []
 
-    def emit(_i: int, tok: int) -> None:
-        pieces.append(tok)
-        if as_ids:
-            print(tok, end=" ", flush=True)
-        else:
-            text = engine.decode(pieces)
-            emit.shown = getattr(emit, "shown", "")
-            if text.startswith(emit.shown) and not text.endswith("�"):     # hold back incomplete UTF-8
-                print(text[len(emit.shown):], end="", flush=True)
-                emit.shown = text
+    def show_id(_i: int, tok: int) -> None:
+        print(tok, end=" ", flush=True)
 
-    res = engine.generate([prompt], opts, on_token=emit)[0]
+    def show_text(_i: int, text: str) -> None:       # whole characters, never a stop string (text.go:16-78)
+        print(text, end="", flush=True)
+
+    res = engine.generate([prompt], opts, on_token=show_id if as_ids else None,
+                          on_text=None if as_ids else show_text)[0]
     print("\n")
     if verbose:
         st = res.stats
@@ -152,7 +147,7 @@ def _repl(engine, opts, verbose: bool) -> int:
         if line.startswith("/"):
             print(f"Unknown command {line.split()[0]}. Type /? for help.")
             continue
-        ids = engine.encode(line) if not history else engine.tokenizer.encode(line, add_special_tokens=False).ids
+        ids = engine.encode(line) if not history else engine.tokenizer.encode(line)
         prompt = history + ids
         if len(prompt) >= engine.max_context:
             print("Error: the conversation no longer fits the context window; /clear starts over", file=sys.stderr)
@@ -187,6 +182,8 @@ def cmd_show(argv: List[str]) -> int:
     spec = arch.build_spec(cfg)
     params = 0
     for need in model_tensor_needs(spec).values():
+        if need.optional:               # a head of its own that a tied model may store but does not need
+            continue
         n = 1
         for s in need.shape:
             n *= s

@@ -70,16 +70,23 @@ def _freeze(v: Any) -> Any:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: which parts it is made of and where its tensors are in the file.
+    """One layer: its block arrangement, the parts the block is made of, and where the parts'
+    tensors are in the file.
 
-    ``names`` maps a part-local tensor key (``"mixer.q"``, ``"ffn.down"``,
-    ``"mixer_norm.weight"`` ...) to the tensor's name in the checkpoint."""
+    ``parts`` maps a key of the block's choosing (``"mixer"``, ``"ffn"``, ``"mixer_norm"`` ...) to
+    (category, spec); the block kind says which keys it asks for.  ``names`` maps a part-local
+    tensor key (``"mixer.q"``, ``"ffn.down"``, ``"mixer_norm.weight"`` ...: the part's key, a dot,
+    the tensor's key within the part) to the tensor's name in the checkpoint."""
     block: PartSpec
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    parts: Mapping[str, Tuple[str, PartSpec]]
     names: Mapping[str, str] = field(default_factory=dict)
+
+    @classmethod
+    def pre_norm(cls, block: PartSpec, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                 ffn_norm: PartSpec, names: Optional[Mapping[str, str]] = None) -> "LayerSpec":
+        """The four parts of a block with a norm in front of its mixer and of its feed-forward."""
+        return cls(block, {"mixer": ("mixer", mixer), "ffn": ("feed_forward", feed_forward),
+                           "mixer_norm": ("norm", mixer_norm), "ffn_norm": ("norm", ffn_norm)}, dict(names or {}))
 
 
 @dataclass(frozen=True)
@@ -109,6 +116,9 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     max_positions: int = 2048
+    # name patterns (fnmatch) of tensors that files of this architecture may carry without any part
+    # asking for them; they are skipped with a warning instead of failing the load
+    ignorable: Tuple[str, ...] = ()
 
     @staticmethod
     def sequential(n_layers: int) -> Tuple[RunSpec, ...]:

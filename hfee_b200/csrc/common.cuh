@@ -38,6 +38,9 @@ int hfee_check_launch(const char* what);
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Streaming multiprocessors of the current device; 0 if the query fails (launchers then refuse).
+extern "C" int hfee_sm_count();
+
 // 0 when the environment variable HFEE_NO_PDL is set.
 int hfee_pdl_enabled();
 

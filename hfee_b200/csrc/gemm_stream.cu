@@ -637,13 +637,8 @@ int launch_wide(const void* A, long long lda, const void* W, long long ldw, void
                 int epilogue, int M, int N, int K, cudaStream_t stream) {
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-  }
+  const int sms = hfee_sm_count();
+  if (sms <= 0) return hfee_fail(HFEE_ERR_CUDA, "gemm_stream: cannot ask the device for its number of SMs");
   const int n_tiles = (N + 7) / 8;
   unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
   constexpr int RED_BYTES = WD_WARPS * 16 * SL_TOKEN_PITCH * 4;
@@ -674,13 +669,8 @@ int launch_slices(const void* A, long long lda, const void* W, long long ldw, vo
                   int epilogue, int M, int N, int K, const NormArgs& norm, cudaStream_t stream) {
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-  static int resident = 0;
-  if (resident == 0) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    resident = 2 * (sms > 0 ? sms : 148);
-  }
+  const int resident = 2 * hfee_sm_count();
+  if (resident <= 0) return hfee_fail(HFEE_ERR_CUDA, "gemm_stream: cannot ask the device for its number of SMs");
   const int n_tiles = (N + 7) / 8;
   unsigned grid = (unsigned)(n_tiles < resident ? n_tiles : resident);
 #define HFEE_GO(EPI, T) hfee_launch(gemm_stream_slices_kernel<EPI, NORM, T>, dim3(grid), dim3(SL_WARPS * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K, norm)
@@ -703,11 +693,10 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   static int resident = 0;                       // CTAs of this instantiation the whole GPU holds at once
   if (resident == 0) {
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int per_sm = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<MT, NT, NW, EPI_STORE, float>, NW * 32, 0);
-    resident = (sms > 0 ? sms : 148) * (per_sm > 0 ? per_sm : 1);
+    resident = hfee_sm_count() * (per_sm > 0 ? per_sm : 1);
+    if (resident <= 0) return hfee_fail(HFEE_ERR_CUDA, "gemm_stream: cannot ask the device for its number of SMs");
   }
   int n_tiles = (N + 8 * NT - 1) / (8 * NT);
   unsigned grid = (unsigned)(n_tiles < resident ? n_tiles : resident);
@@ -734,7 +723,9 @@ int launch_rows(const void* A, long long lda, const void* W, long long ldw, void
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   int n_tiles = (N + 7) / 8;
   int ctas = (n_tiles + ROWS_WARPS - 1) / ROWS_WARPS;
-  unsigned grid = (unsigned)(ctas < 2 * 148 ? ctas : 2 * 148);
+  const int resident = 2 * hfee_sm_count();              // two CTAs of this kernel share an SM
+  if (resident <= 0) return hfee_fail(HFEE_ERR_CUDA, "gemm_stream: cannot ask the device for its number of SMs");
+  unsigned grid = (unsigned)(ctas < resident ? ctas : resident);
 #define HFEE_GO(EPI, T) hfee_launch(gemm_stream_rows_kernel<MT, EPI, T>, dim3(grid), dim3(ROWS_WARPS * 32), 0, stream, a, lda, w, ldw, (T*)C, ldc, M, N, K)
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_stream: accumulate needs a float32 output");

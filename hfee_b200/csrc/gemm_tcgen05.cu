@@ -427,13 +427,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e));
     configured = true;
   }
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-  }
+  const int sms = hfee_sm_count();
+  if (sms <= 0) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05: cannot ask the device for its number of SMs");
   long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sk_ctas = (workspace && flags) ? plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, BN) : 0;
   dim3 grid((unsigned)(sk_ctas ? sk_ctas : (tiles < sms ? tiles : sms)));          // one CTA per SM
@@ -491,10 +486,8 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
 
 // How many CTAs hfee_gemm_tcgen05 would split this shape's K blocks among (0: whole tiles per CTA).
 HFEE_API int hfee_gemm_tcgen05_stream_k(int M, int N, int K, int block_n, long long workspace_floats) {
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (sms <= 0) sms = 148;
+  const int sms = hfee_sm_count();
+  if (sms <= 0) return 0;
   long long tiles = (long long)((M + BM - 1) / BM) * ((N + block_n - 1) / block_n);
   return plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, block_n);
 }

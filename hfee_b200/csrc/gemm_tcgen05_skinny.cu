@@ -277,16 +277,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restr
   }
 }
 
-int device_sms() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-  }
-  return sms;
-}
+int device_sms() { return hfee_sm_count(); }
 
 // K split for N weight rows and K: as many CTAs as SMs, at least 4 K blocks each.
 void plan_split(int N, int K, int M, long long workspace_floats, int* splits, int* kb_per_split) {

@@ -29,6 +29,17 @@ HFEE_API int hfee_device_is_sm100() {
   return major == 10;
 }
 
+// Streaming multiprocessors of the current device (asked once per device); 0 if the query fails.
+HFEE_API int hfee_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
+  if (dev >= 0 && dev < 64) cached[dev] = sms;
+  return sms;
+}
+
 int hfee_pdl_enabled() {
   static int enabled = -1;
   if (enabled < 0) enabled = getenv("HFEE_NO_PDL") == nullptr ? 1 : 0;

@@ -92,7 +92,7 @@ class ModelRunner:
         cache.sync()
         step = Step(entries, cache.length, self.buffers)
         step.feedback = self.feedback
-        if (self.engine.use_cuda_graphs and self.device.type == "cuda" and step.decode_only
+        if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
                 and all(tuple(e.want) == (0,) for e in entries)):
             logits = self._graphed_forward(step)
         else:

@@ -104,18 +104,31 @@ class Scheduler:
         self.waiting.append(request)
 
     def abort(self, request: Request) -> None:
+        """Cancel a request wherever it is (runner.go:244-247: a cancelled context ends the
+        request before its next pass).  What it holds goes back at once; tokens that were sampled
+        on the device and not read back yet are dropped from its output."""
         if request.finished:
             return
-        if request in self.running:
-            self._finish(request, FinishReason.ABORT)
-        else:
-            self.waiting.remove(request)
-            request.finished = request.stats.done_reason = FinishReason.ABORT
-            self._done.append(request)
+        self.cut(request, len(request.output), FinishReason.ABORT)
 
     def finish(self, request: Request, reason: str) -> None:
-        """End a running request from outside (a stop string matched, say)."""
+        """End a running request from outside."""
         if not request.finished:
+            self._finish(request, reason)
+
+    def cut(self, request: Request, keep: int, reason: str) -> None:
+        """End ``request`` with ``reason`` keeping its first ``keep`` output tokens (a stop string
+        began behind them, runner.go:306-308).  Placeholders of tokens not read back yet go in any
+        case; like the reference, tokens that were sampled still count in ``eval_tokens``."""
+        out = request.output
+        while out and out[-1] == DEVICE_TOKEN:
+            out.pop()
+            request.stats.eval_tokens -= 1
+        del out[keep:]
+        request.feed = []
+        if request.finished:
+            request.finished = request.stats.done_reason = reason
+        else:
             self._finish(request, reason)
 
     @property
@@ -277,7 +290,7 @@ class Scheduler:
         dropped (the reference does not emit or count the end token, runner.go:288-291)."""
         for (req, idx), tok in zip(pending, tokens):
             if idx >= len(req.output):
-                continue                                  # cut off by an end token found earlier
+                continue                                  # cut off by an end token, a stop string or a cancel
             tok = int(tok)
             if tok in self.eos:
                 dropped = len(req.output) - idx

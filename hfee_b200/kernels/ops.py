@@ -63,6 +63,7 @@ def library() -> ctypes.CDLL:
         raise KernelLibraryError(f"cannot load the sm_100a kernel library: {e}") from e
     lib.hfee_last_error.restype = ctypes.c_char_p
     lib.hfee_device_is_sm100.restype = _I
+    lib.hfee_sm_count.restype = _I
     lib.hfee_gemm_skinny_splits.restype = _I
     lib.hfee_attention_tc_supports.restype = _I
     for name, sig in _SIGNATURES.items():
@@ -77,6 +78,14 @@ def library() -> ctypes.CDLL:
         raise KernelLibraryError(f"the kernels are built for sm_100a only; this device is sm_{major}{minor}")
     _LIB = lib
     return lib
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, as the kernels' launchers see them."""
+    n = library().hfee_sm_count()
+    if n <= 0:
+        raise KernelLibraryError("cannot ask the device for its number of SMs")
+    return n
 
 
 def loaded_library_path() -> Optional[str]:
@@ -213,7 +222,6 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
 
 STREAM_MAX_TOKENS = 64
 USE_TCGEN05 = True
-SM_COUNT = 148
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
 
 
@@ -276,7 +284,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         # 192 wide where that saves a round of tiles: 16 x 12 tiles of 256 are two rounds on 148 SMs
         # with the second a third full, 16 x 16 tiles of 192 are two rounds of three quarters the work
         if block_n == 256 and n % 192 == 0:
-            rounds = lambda bn: -(-(-(-m // 128) * -(-n // bn)) // SM_COUNT)
+            rounds = lambda bn: -(-(-(-m // 128) * -(-n // bn)) // sm_count())
             if rounds(192) * 192 * 1.05 < rounds(256) * 256:
                 block_n = 192
     if stream_k is None:
@@ -297,8 +305,8 @@ def _stream_k_workspace():
     two flag words per SM (zero at the start; every launch leaves them zero).  Made once, 19 MiB."""
     global _STREAM_K_WS
     if _STREAM_K_WS is None:
-        _STREAM_K_WS = (torch.empty(SM_COUNT * 128 * 256, dtype=torch.float32, device="cuda"),
-                        torch.zeros(2 * SM_COUNT, dtype=torch.int32, device="cuda"))
+        _STREAM_K_WS = (torch.empty(sm_count() * 128 * 256, dtype=torch.float32, device="cuda"),
+                        torch.zeros(2 * sm_count(), dtype=torch.int32, device="cuda"))
     return _STREAM_K_WS
 
 
@@ -455,14 +463,14 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
 MAX_SPLITS = 32
 
 
-def attention_splits(requests: int, kv_heads: int, max_context: int) -> int:
+def attention_splits(requests: int, kv_heads: int, max_context: int, sms: Optional[int] = None) -> int:
     """How many CTAs share the keys of one (request, kv head) in a decode step: about four CTAs
     per SM in all (measured alone at batch 8: 9 splits against 6 take 10.3 / 27.2 / 90.8 us against
     11.3 / 30.9 / 99.6 us at 2,048 / 8,192 / 32,768 keys; batch 12 at 8,192 keys: 6 against 4 take
     37.5 against 42.6 us), and at least four even when the batch alone would fill the GPU (shorter
     CTAs balance better and keep more loads in flight: at 2,048 keys, batch 32: 41.8 us unsplit,
     33.4 us with four), but at least two key blocks of 64 each."""
-    want = max(4, 4 * SM_COUNT // max(1, requests * kv_heads))
+    want = max(4, 4 * (sms or sm_count()) // max(1, requests * kv_heads))
     return max(1, min(MAX_SPLITS, want, max_context // 128))
 
 
@@ -614,6 +622,7 @@ _SAMPLE_SCRATCH: Optional[torch.Tensor] = None
 CHAIN_MAX_K = 64            # largest top-k the device chain takes
 CHAIN_HISTORY = 256         # tokens of recent history kept per request slot for the repeat penalty
 CHAIN_CHUNK = 2048
+CHAIN_MAX_VOCAB = 128 * CHAIN_CHUNK     # the chain kernels look at no more chunks than this; larger vocabularies take the host chain
 
 
 def chain_scratch_floats(rows: int, vocab: int) -> int:

@@ -25,7 +25,7 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        layers.append(LayerSpec(block=block, mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm, names={
+        layers.append(LayerSpec.pre_norm(block, mixer, ffn, norm, norm, names={
             "mixer.q": p + "self_attn.q_proj.weight", "mixer.k": p + "self_attn.k_proj.weight",
             "mixer.v": p + "self_attn.v_proj.weight", "mixer.o": p + "self_attn.o_proj.weight",
             "ffn.gate": p + "mlp.gate_proj.weight", "ffn.up": p + "mlp.up_proj.weight",
@@ -43,6 +43,7 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
         head=PartSpec("linear", vocab=cfg.vocab_size, width=cfg.hidden_size, tied=cfg.tie_word_embeddings),
         names=names, eos_token_ids=cfg.eos_token_ids, bos_token_id=cfg.bos_token_id,
         max_positions=cfg.max_position_embeddings,
+        ignorable=("*.rotary_emb.inv_freq",),             # a buffer that older exports store beside the weights
     )
 
 

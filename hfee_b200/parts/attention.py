@@ -26,6 +26,10 @@ class PagedAttention(Mixer):
 
     accepts_lazy_input = True        # the input norm may be fused into the q/k/v projection
 
+    @property
+    def graph_safe(self) -> bool:    # every launch reads the batch from device buffers; the position part decides
+        return bool(self.position.graph_safe)
+
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
         q, kv = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim

@@ -12,11 +12,17 @@ Categories and what each must provide:
 ``mixer``         ``cache_need()`` and ``forward(xn[n,w], residual_f32[n,w], step, cache, writes_cache)``
                   (adds its output into ``residual``)
 ``feed_forward``  ``forward(xn[n,w], residual_f32[n,w], step)`` (adds into ``residual``)
-``block``         ``forward(residual_f32[n,w], step, cache, writes_cache)``, arranging the above
+``block``         ``forward(residual_f32[n,w], step, cache, writes_cache)``, arranging the above; it is
+                  built with ``parts={key: part}`` for the keys its layer spec names
 ``embedding``     ``forward(step, residual_f32[n,w])``
 ``head``          ``forward(xn[m,w], logits_f32[m,vocab])``
 
-Every part class has ``tensor_needs(spec) -> {local key: TensorNeed}``.
+Every part class has ``tensor_needs(spec) -> {local key: TensorNeed}`` and the flag
+``graph_safe``: True says that ``forward`` launches the same kernels on the same buffers for every
+decode-only step of a given batch size and takes everything that changes from step to step (slots,
+positions, lengths, block tables) from device memory, so such a step may be captured in a CUDA
+graph and replayed.  A part that reads the step's host-side lists leaves it False, and a model
+with such a part always runs eagerly.
 """
 from __future__ import annotations
 
@@ -78,6 +84,7 @@ class Runtime:
 
 class Part:
     category: str = ""
+    graph_safe: bool = False
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
@@ -96,6 +103,32 @@ class Mixer(Part):
         return None
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of a layer's parts.  ``needs`` lists the keys it asks of ``LayerSpec.parts``;
+    the model builds those parts and hands them over as ``parts``."""
+    category = "block"
+    needs: Tuple[str, ...] = ()
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime, parts: Mapping[str, Part]):
+        super().__init__(spec, tensors, rt)
+        missing = [k for k in self.needs if k not in parts]
+        if missing:
+            raise ValueError(f"block {spec.kind!r} needs the parts {list(self.needs)}; the layer gives no {missing}")
+        self.parts = dict(parts)
+
+    def cache_need(self):
+        """What the layer caches per request: its mixer's need, if it has a part called ``mixer``."""
+        mixer = self.parts.get("mixer")
+        return mixer.cache_need() if mixer is not None else None
+
+    @property
+    def all_graph_safe(self) -> bool:
+        return bool(self.graph_safe) and all(p.graph_safe for p in self.parts.values())
+
+    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
         raise NotImplementedError
 
 

@@ -5,20 +5,21 @@ from typing import Any
 
 import torch
 
-from .base import Part, register_part
+from .base import Block, register_part
 from .norm import LazyNormed
 
 
-class PreNormBlock(Part):
+class PreNormBlock(Block):
     """``x += mixer(norm(x)); x += feed_forward(norm(x))`` on the float32 residual
     stream (hostfog/hfee internal/llm/forward.go:82-114).  Built by the model with
     its four parts already constructed."""
-    category = "block"
+    needs = ("mixer", "ffn", "mixer_norm", "ffn_norm")
+    graph_safe = True
 
-    def __init__(self, spec, tensors, rt, mixer=None, feed_forward=None, mixer_norm=None, ffn_norm=None):
-        super().__init__(spec, tensors, rt)
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+    def __init__(self, spec, tensors, rt, parts):
+        super().__init__(spec, tensors, rt, parts)
+        self.mixer, self.feed_forward = parts["mixer"], parts["ffn"]
+        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts["ffn_norm"]
         self.width = int(spec.width)
 
     def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:

@@ -15,6 +15,7 @@ class TokenEmbedding(Part):
     """``x[i,:] = table[token_i,:]``, unscaled (hostfog/hfee internal/llm/forward.go:75-77).
     spec: ``vocab``, ``width``."""
     category = "embedding"
+    graph_safe = True
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
@@ -32,6 +33,7 @@ class LinearHead(Part):
     """``logits = x . W^T`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
     ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121)."""
     category = "head"
+    graph_safe = True
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:

@@ -15,6 +15,7 @@ from .base import Part, register_part
 class SwiGLUFeedForward(Part):
     """spec: ``width``, ``inner`` (intermediate size)."""
     category = "feed_forward"
+    graph_safe = True
     accepts_lazy_input = True        # the input norm may be fused into the gate/up projection
 
     @staticmethod

@@ -17,13 +17,6 @@ from ..weights.loader import Checkpoint, TensorNeed
 from .base import Runtime, build_part, part_class
 from .norm import LazyNormed
 
-_LAYER_PARTS = (("mixer", "mixer"), ("feed_forward", "ffn"), ("norm", "mixer_norm"), ("norm", "ffn_norm"))
-
-
-def _layer_part_specs(layer: LayerSpec) -> Dict[str, Tuple[str, PartSpec]]:
-    return {"mixer": ("mixer", layer.mixer), "ffn": ("feed_forward", layer.feed_forward),
-            "mixer_norm": ("norm", layer.mixer_norm), "ffn_norm": ("norm", layer.ffn_norm)}
-
 
 def _named(needs: Mapping[str, TensorNeed], prefix: str, names: Mapping[str, str], where: str) -> Dict[str, Tuple[str, TensorNeed]]:
     out = {}
@@ -46,7 +39,7 @@ def _collect(spec: ModelSpec) -> Tuple[Dict[str, Tuple[str, TensorNeed]], List[D
     layers = []
     for i, layer in enumerate(spec.layers):
         m: Dict[str, Tuple[str, TensorNeed]] = {}
-        for prefix, (cat, ps) in _layer_part_specs(layer).items():
+        for prefix, (cat, ps) in layer.parts.items():
             m.update(_named(part_class(cat, ps.kind).tensor_needs(ps), prefix, layer.names, f"layer {i}"))
         layers.append(m)
     return top, layers
@@ -68,7 +61,7 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, checkpoint: Checkpoint, rt: Runtime):
         check_schedule(spec.layers, spec.schedule)
         self.spec, self.rt = spec, rt
-        checkpoint.check(model_tensor_needs(spec))
+        checkpoint.check(model_tensor_needs(spec), spec.ignorable)
         top, layers = _collect(spec)
 
         def fetch(m: Mapping[str, Tuple[str, TensorNeed]], prefix: str) -> Dict[str, torch.Tensor]:
@@ -83,18 +76,18 @@ class DecoderModel:
         self.head = part_class("head", spec.head.kind)(spec.head, fetch(top, "head"), rt, embedding=self.embedding)
         self.blocks = []
         for layer, m in zip(spec.layers, layers):
-            parts = {prefix: build_part(cat, ps, fetch(m, prefix), rt)
-                     for prefix, (cat, ps) in _layer_part_specs(layer).items()}
-            self.blocks.append(part_class("block", layer.block.kind)(
-                layer.block, {}, rt, mixer=parts["mixer"], feed_forward=parts["ffn"],
-                mixer_norm=parts["mixer_norm"], ffn_norm=parts["ffn_norm"]))
+            parts = {prefix: build_part(cat, ps, fetch(m, prefix), rt) for prefix, (cat, ps) in layer.parts.items()}
+            self.blocks.append(part_class("block", layer.block.kind)(layer.block, {}, rt, parts=parts))
         self.width, self.vocab = spec.width, spec.vocab
+        # decode steps may be captured in CUDA graphs only if every part of the schedule allows it
+        self.graph_safe = (self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
+                           and all(self.blocks[run.layer].all_graph_safe for run in spec.schedule))
 
     def cache_needs(self) -> Dict[int, Any]:
         """cache id -> what the writing run's mixer needs (PagedKV, FixedState or None)."""
         out: Dict[int, Any] = {}
         for run in self.spec.schedule:
-            need = self.blocks[run.layer].mixer.cache_need()
+            need = self.blocks[run.layer].cache_need()
             if run.writes_cache:
                 out[run.cache] = need
             elif out.get(run.cache) != need:

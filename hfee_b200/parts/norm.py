@@ -16,6 +16,7 @@ from .base import Part, register_part
 class RMSNorm(Part):
     """spec: ``width``, ``eps``, ``add_unit`` (scale by 1+w instead of w; default False)."""
     category = "norm"
+    graph_safe = True
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:

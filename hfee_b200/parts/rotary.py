@@ -27,6 +27,7 @@ class Rotary(Part):
     (a RopeScaling or None) and ``pairing``: ``"half"`` rotates (i, i+rope_dim/2),
     ``"interleaved"`` rotates (2i, 2i+1) as internal/llm/forward.go:187-190 does."""
     category = "position"
+    graph_safe = True
 
     def __init__(self, spec, tensors, rt):
         super().__init__(spec, tensors, rt)
@@ -56,6 +57,7 @@ class Rotary(Part):
 class NoPosition(Part):
     """No position encoding: queries and keys are cached as projected."""
     category = "position"
+    graph_safe = True
     rope_dim = 0
     interleaved = False
 

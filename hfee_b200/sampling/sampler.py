@@ -129,6 +129,10 @@ class BatchSampler:
         self.row_history = torch.zeros(max_rows, ops.CHAIN_HISTORY, dtype=torch.int32, device=self.device)
         self.row_history_len = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
         self.rows = torch.arange(max_rows, dtype=torch.int32, device=self.device)
+        # pinned staging for the rings of requests that start (or come back after a preemption)
+        self.ring_host = [torch.zeros(ops.CHAIN_HISTORY + 1, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
+        self.ring_events = [None] * 4
+        self.ring_turn = 0
 
     @staticmethod
     def _chain_params(o: SamplingOptions, u: float) -> List[float]:
@@ -143,12 +147,28 @@ class BatchSampler:
             self.chain_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
         return self.chain_scratch
 
+    def chain_takes(self, vocab: int) -> bool:
+        """Whether the device chain can run over a vocabulary of this size."""
+        return self.use_device_chain and vocab <= ops.CHAIN_MAX_VOCAB
+
     def load_history(self, slot: int, tokens: Sequence[int]) -> None:
-        """Start the ring of recent tokens of the request in ``slot`` from its tokens so far."""
-        tail = [int(t) for t in tokens[-ops.CHAIN_HISTORY:]]
-        if tail:
-            self.history[slot, :len(tail)].copy_(torch.tensor(tail, dtype=torch.int32))
-        self.history_len[slot:slot + 1].fill_(len(tail))
+        """Start the ring of recent tokens of the request in ``slot`` from its tokens so far.  The
+        tokens and their count go through pinned staging rows used in turn, so the host does not
+        wait for the GPU (this runs in the steps that are meant to run ahead of it)."""
+        tail = np.asarray(tokens[-ops.CHAIN_HISTORY:], dtype=np.int32)
+        i = self.ring_turn
+        self.ring_turn = (i + 1) % len(self.ring_host)
+        if self.ring_events[i] is not None:
+            self.ring_events[i].synchronize()            # that staging row's last upload is done
+        host = self.ring_host[i]
+        host[:len(tail)] = torch.from_numpy(tail)
+        host[ops.CHAIN_HISTORY] = len(tail)
+        self.history[slot].copy_(host[:ops.CHAIN_HISTORY], non_blocking=True)
+        self.history_len[slot:slot + 1].copy_(host[ops.CHAIN_HISTORY:], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.ring_events[i] = ev
 
     def sample(self, logits: torch.Tensor, options: Sequence[SamplingOptions], seeds: Sequence[int],
                draws: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
@@ -157,7 +177,7 @@ class BatchSampler:
         m = logits.shape[0]
         assert m == len(options) <= self.max_rows
         us = [uniform(seeds[i], 0, draws[i]) if options[i].temperature > 0 else 0.0 for i in range(m)]
-        if (self.use_device_chain and self.device.type == "cuda" and not all(o.device_only for o in options)
+        if (self.chain_takes(logits.shape[1]) and self.device.type == "cuda" and not all(o.device_only for o in options)
                 and all(o.device_chain for o in options)):
             # the whole chain on the device; the host knows every row's history here, so the rings of
             # recent tokens are simply written anew (rows stand in for request slots)
@@ -204,9 +224,8 @@ class BatchSampler:
         out = self.outs[b][:m]
         if not simple:
             host = self.params_host[b]
-            for i, o in enumerate(options):
-                u = uniform(seeds[i], 0, draws[i]) if o.temperature > 0 else 0.0
-                host[i] = torch.tensor(self._chain_params(o, u), dtype=torch.float64)
+            host.numpy()[:m] = [self._chain_params(o, uniform(seeds[i], 0, draws[i]) if o.temperature > 0 else 0.0)
+                                for i, o in enumerate(options)]
             self.params[:m].copy_(host[:m], non_blocking=True)
             ops.sample_chain(logits, self.params[:m], out, self._chain_scratch(logits.shape[1]), slots, feedback, self.history,
                              self.history_len, penalise=any(o.penalises for o in options))

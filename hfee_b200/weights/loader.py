@@ -8,8 +8,10 @@ names everything missing, unexpected and mis-shaped.
 """
 from __future__ import annotations
 
+import fnmatch
+import warnings
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Mapping, Optional, Tuple
+from typing import Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -59,10 +61,16 @@ _FLOATS = (torch.float32, torch.float16, torch.bfloat16, torch.float64)
 _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
 
 
-def check_tensors(needs: Mapping[str, TensorNeed],
-                  have: Mapping[str, Tuple[torch.dtype, Tuple[int, ...]]]) -> None:
+def check_tensors(needs: Mapping[str, TensorNeed], have: Mapping[str, Tuple[torch.dtype, Tuple[int, ...]]],
+                  ignorable: Sequence[str] = ()) -> List[str]:
+    """Compare what the parts ask for with what the files hold; raises ONE :class:`WeightError`
+    for everything missing, unexpected, mis-shaped or of an unusable dtype.  Tensors nobody asked
+    for whose names match one of the ``ignorable`` patterns (buffers that exporters store beside the
+    weights, named by the architecture) are returned instead of counted as unexpected."""
     missing = [n for n, need in needs.items() if n not in have and not need.optional]
-    unexpected = [n for n in have if n not in needs]
+    extra = [n for n in have if n not in needs]
+    ignored = [n for n in extra if any(fnmatch.fnmatchcase(n, pat) for pat in ignorable)]
+    unexpected = [n for n in extra if n not in set(ignored)]
     wrong_shape = []
     wrong_dtype = []
     for n, need in needs.items():
@@ -76,6 +84,7 @@ def check_tensors(needs: Mapping[str, TensorNeed],
             wrong_dtype.append((n, str(dtype)))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(sorted(missing), sorted(unexpected), sorted(wrong_shape), sorted(wrong_dtype))
+    return sorted(ignored)
 
 
 def kept_dtype(need: TensorNeed, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
@@ -95,9 +104,12 @@ class Checkpoint:
     def __init__(self, model_dir: str):
         self.files = TensorFiles(model_dir)
 
-    def check(self, needs: Mapping[str, TensorNeed]) -> None:
+    def check(self, needs: Mapping[str, TensorNeed], ignorable: Sequence[str] = ()) -> None:
         have = {n: (self.files.info(n).dtype, self.files.info(n).shape) for n in self.files.names()}
-        check_tensors(needs, have)
+        ignored = check_tensors(needs, have, ignorable)
+        if ignored:
+            shown = ", ".join(ignored[:4]) + (", ..." if len(ignored) > 4 else "")
+            warnings.warn(f"{len(ignored)} tensors of the checkpoint are not used by the model and were skipped: {shown}")
 
     def has(self, name: str) -> bool:
         return name in self.files

@@ -80,6 +80,54 @@ def mixed(seqs, live=4, seed=0, chunk_sizes=(2, 3, 5, 9, 16, 31)):
     return steps
 
 
+def batched_decode(seqs, tails, live=None, want_head="all"):
+    """Every request's head (all but its last ``tails[i]`` tokens) in a step of its own, then
+    decode-only steps that give every live request one token.  Requests end after their last
+    token, so with different tails the batch shrinks step by step; with ``live`` smaller than
+    ``len(seqs)`` the waiting requests join as others leave (their head in a step of its own
+    between the decode steps, in the slot that just became free).  ``want_head``: "all" asks for
+    the logits of every head position, "last" for the last one only."""
+    live = live or len(seqs)
+    waiting = list(range(len(seqs)))
+    active = {}
+    steps = []
+    while waiting or active:
+        while waiting and len(active) < live:
+            rid = waiting.pop(0)
+            head = max(len(seqs[rid]) - tails[rid], 1)
+            want = list(range(head)) if want_head == "all" else [head - 1]
+            done = head == len(seqs[rid])
+            steps.append({"entries": [(rid, seqs[rid][:head], want)], "end": [rid] if done else []})
+            if not done:
+                active[rid] = head
+        if not active:
+            continue
+        entries, end = [], []
+        for rid in list(active):
+            at = active[rid]
+            entries.append((rid, seqs[rid][at:at + 1], [0]))
+            active[rid] = at + 1
+            if at + 1 == len(seqs[rid]):
+                end.append(rid)
+                del active[rid]
+        steps.append({"entries": entries, "end": end})
+    return steps
+
+
+def expected_rows(refs, steps):
+    """For traces that do not ask for every position: {rid: reference rows in the order the trace
+    asks for them}."""
+    at = {}
+    out = {}
+    for st in steps:
+        for rid, toks, want in st["entries"]:
+            base = at.get(rid, 0)
+            for w in want:
+                out.setdefault(rid, []).append(refs[rid][base + w])
+            at[rid] = base + len(toks)
+    return {rid: np.stack(v) for rid, v in out.items()}
+
+
 def run_in_process(runner, steps):
     """Feed a trace to a ModelRunner; returns {rid: [logits rows in position order]}."""
     from hfee_b200 import StepEntry

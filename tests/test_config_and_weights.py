@@ -80,9 +80,12 @@ def test_llama3_scaling_bands():
 def test_spec_is_data_and_schedule_is_checked():
     spec = llama_spec(LlamaConfig.from_dict(TINY_A))
     assert len(spec.layers) == 2 and [r.layer for r in spec.schedule] == [0, 1]
-    assert spec.layers[0].mixer.kind == "attention" and spec.layers[0].mixer.position.kind == "rotary"
-    assert spec.layers[0].mixer == spec.layers[1].mixer and hash(spec.layers[0].mixer) == hash(spec.layers[1].mixer)
-    assert spec.layers[0].mixer.replace(window=8) != spec.layers[0].mixer
+    assert sorted(spec.layers[0].parts) == ["ffn", "ffn_norm", "mixer", "mixer_norm"]       # a layer's parts are data
+    category, mixer = spec.layers[0].parts["mixer"]
+    assert category == "mixer" and mixer.kind == "attention" and mixer.position.kind == "rotary"
+    assert spec.layers[0].parts["ffn"] == ("feed_forward", spec.layers[1].parts["ffn"][1])
+    assert mixer == spec.layers[1].parts["mixer"][1] and hash(mixer) == hash(spec.layers[1].parts["mixer"][1])
+    assert mixer.replace(window=8) != mixer
     check_schedule(spec.layers, [RunSpec(0, 0), RunSpec(1, 1), RunSpec(1, 2), RunSpec(0, 0, writes_cache=False)])
     with pytest.raises(ValueError, match="already has a writer"):
         check_schedule(spec.layers, [RunSpec(0, 0), RunSpec(1, 0)])
@@ -109,6 +112,30 @@ def test_tensor_needs_cover_the_checkpoint_names():
     assert "lm_head.weight" not in model_tensor_needs(unnamed) and len(model_tensor_needs(unnamed)) == 2 + 3 * 9
     with pytest.raises(ValueError, match="no checkpoint name"):
         model_tensor_needs(dataclasses.replace(spec, names={k: v for k, v in spec.names.items() if k != "final_norm.weight"}))
+
+
+def test_buffers_the_architecture_names_as_ignorable_are_skipped_with_a_warning(tmp_path):
+    """Older exports store ``rotary_emb.inv_freq`` beside every layer's weights: the load goes through
+    and says what it skipped; any other stranger still fails, in the same single error."""
+    d = str(tmp_path / "m")
+    write_random_model(d, TINY_A, seed=0)
+    files = TensorFiles(d)
+    tensors = {n: files.tensor(n).clone() for n in files.names()}
+    for i in range(2):
+        tensors[f"model.layers.{i}.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_file(os.path.join(d, "model.safetensors"), tensors)
+    spec = llama_spec(LlamaConfig.from_dict(TINY_A))
+    assert spec.ignorable == ("*.rotary_emb.inv_freq",)
+    with pytest.warns(UserWarning, match="2 tensors of the checkpoint are not used"):
+        Checkpoint(d).check(model_tensor_needs(spec), spec.ignorable)
+    with pytest.raises(WeightError) as e:
+        Checkpoint(d).check(model_tensor_needs(spec))                      # without the patterns they are strangers
+    assert len(e.value.unexpected) == 2
+    tensors["model.layers.0.self_attn.something_else"] = torch.zeros(3)
+    write_file(os.path.join(d, "model.safetensors"), tensors)
+    with pytest.raises(WeightError) as e:
+        Checkpoint(d).check(model_tensor_needs(spec), spec.ignorable)
+    assert e.value.unexpected == ["model.layers.0.self_attn.something_else"]
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):

@@ -31,10 +31,10 @@ class Batch:
         self.k = [torch.randn(t, kv, hd, generator=g).to(dtype) for t in total]
         self.v = [torch.randn(t, kv, hd, generator=g).to(dtype) for t in total]
         for i in range(r):
-            for pos in range(total[i]):
-                pg = int(perm[i, pos // page])
-                self.kp[pg, :, pos % page] = self.k[i][pos].to(DEV)
-                self.vp[pg, :, pos % page] = self.v[i][pos].to(DEV)
+            for first in range(0, total[i], page):                 # a page at a time
+                pg, m = int(perm[i, first // page]), min(page, total[i] - first)
+                self.kp[pg, :, :m] = self.k[i][first:first + m].transpose(0, 1).to(DEV)
+                self.vp[pg, :, :m] = self.v[i][first:first + m].transpose(0, 1).to(DEV)
         n = sum(new)
         self.q = (torch.randn(n, heads * hd, generator=g) * q_scale).to(dtype).to(DEV)
         cu = np.concatenate([[0], np.cumsum(new)])
@@ -122,6 +122,41 @@ def test_attention_split_keys(heads, kv, hd, page, splits):
     ops.attention_mma(b.q, b.kp, b.vp, b.table, page, b.cu_tokens, b.slots, b.context_before, out, b.n, b.r, 1,
                       heads, kv, hd, scale, 0, splits, scratch)
     assert _err(out, b.reference(scale)) < 1e-2
+
+
+@pytest.mark.parametrize("batch", [1, 8, 64])
+@pytest.mark.parametrize("heads,kv,hd", [(32, 8, 64), (8, 2, 128)])
+def test_decode_at_the_contexts_and_splits_of_the_benchmark(batch, heads, kv, hd):
+    """Decode steps at the context lengths the benchmark and long generations reach (a page's and a
+    block's edge at 2,048 and 4,096; 8,191) with the number of key splits the dispatcher picks for
+    batches of 1, 8 and 64, through the fused rotary kernel and through the plain one."""
+    from hfee_b200.kernels import ops
+    page = 64
+    contexts = [2047, 2048, 4095, 4096, 8191]
+    shown = min(batch, len(contexts))            # requests whose rows are checked; the dispatcher plans for `batch`
+    before = contexts[:shown]
+    b = Batch(torch.bfloat16, heads, kv, hd, page, before, [1] * shown, seed=batch + hd)
+    scale = 1 / math.sqrt(hd)
+    ref = b.reference(scale)
+    for planned in (max(before) + 1, 8192):     # planned for the longest context now, or for the engine's limit
+        splits = ops.attention_splits(batch, kv, planned)
+        assert 1 <= splits <= ops.MAX_SPLITS
+        scratch = torch.full((b.n * heads * splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
+        out = torch.full_like(b.q, float("nan"))
+        ops.attention_mma(b.q, b.kp, b.vp, b.table, page, b.cu_tokens, b.slots, b.context_before, out, b.n, b.r, 1,
+                          heads, kv, hd, scale, 0, splits, scratch)
+        assert _err(out, ref) < 1e-2, (splits, planned)
+        # the fused kernel: no rotation (rope_dim 0), so its queries are the rows above and the new key and
+        # value are the ones already in the cache; it rewrites them in place
+        qkv = torch.cat([b.q, torch.stack([b.k[i][-1].reshape(-1) for i in range(b.r)]).to(DEV),
+                         torch.stack([b.v[i][-1].reshape(-1) for i in range(b.r)]).to(DEV)], dim=1).contiguous()
+        b.attention_splits = splits
+        got = torch.full_like(b.q, float("nan"))
+        kp, vp = b.kp.clone(), b.vp.clone()
+        ops.paged_attention_rope(qkv, None, 0, False, True, kp, vp, b.table, page, got, heads, kv, hd, scale, 0, b,
+                                 scratch if splits > 1 else None)
+        assert torch.equal(got, out) and torch.equal(kp, b.kp) and torch.equal(vp, b.vp)
+    b.attention_splits = None
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

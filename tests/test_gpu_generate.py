@@ -52,6 +52,79 @@ def test_greedy_generation_bfloat16_follows_plain_where_the_margin_allows(tiny_d
     assert checked >= 5
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_pipelined_generation_bfloat16_picks_the_plain_top1_where_the_margin_allows(tiny_dirs, name):
+    """Engine.generate in bfloat16 with its defaults (pipelined, tokens fed back on the device, CUDA
+    graphs): along each request's own continuation every token whose plain top-1 margin is clear is
+    the plain argmax, and the callback saw the same tokens."""
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs[name], round_to_bf16=True)
+    prompts = prompts_for(cfg, (5, 40, 17, 33), seed=13)
+    eng = Engine(tiny_dirs[name], dtype="bfloat16", page_size=16, max_requests=4, max_context=128, max_batch_tokens=64)
+    assert eng.pipeline and eng.config.use_cuda_graphs
+    seen = [[] for _ in prompts]
+    res = eng.generate(prompts, SamplingOptions.greedy(num_predict=30), on_token=lambda i, t: seen[i].append(t))
+    assert eng.runner.graph_replays > 20
+    checked = 0
+    for p, r, s in zip(prompts, res, seen):
+        assert len(r.token_ids) == 30 and s == r.token_ids and r.stats.done_reason == "length"
+        ref = plain.forward(cfg, w, p + r.token_ids[:-1])
+        for t, tok in enumerate(r.token_ids):
+            row = ref[len(p) - 1 + t]
+            top = np.sort(row)[-2:]
+            if top[1] - top[0] > 2 * 2e-2 * np.abs(row).max():
+                assert tok == int(np.argmax(row)), (name, t)
+                checked += 1
+    assert checked >= 20
+
+
+class _Letters:
+    """A tokenizer for tests: token id -> one or two letters."""
+
+    def piece(self, t):
+        return (chr(ord("a") + t % 26) + (chr(ord("A") + (t // 26) % 26) if t % 3 == 0 else "")).encode()
+
+    def decode(self, ids):
+        return b"".join(self.piece(t) for t in ids).decode()
+
+    def encode(self, text):
+        raise NotImplementedError
+
+
+def test_stop_string_and_cancel_through_the_pipelined_engine(tiny_dirs):
+    """On the GPU with device-side token feedback: a stop string found one step late cuts the request
+    where it belongs, a cancelled request ends with "abort", the others are untouched, and every
+    page and slot is free afterwards."""
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs["A"])
+    prompts = prompts_for(cfg, (20, 25, 30), seed=21)
+    want = [plain.greedy_generate(cfg, w, p, 16) for p in prompts]
+    tok = _Letters()
+    text0 = tok.decode(want[0])
+    ends = np.cumsum([len(tok.piece(t)) for t in want[0]])
+    at = int(ends[6])
+    stop = text0[at:at + 3]
+    assert text0.find(stop) == at
+    eng = Engine(tiny_dirs["A"], tokenizer=tok, dtype="float32", page_size=16, max_requests=3, max_context=128,
+                 max_batch_tokens=64)
+    assert eng.pipeline
+    shown = ["", "", ""]
+
+    def on_text(i, s):
+        shown[i] += s
+
+    opts = [SamplingOptions.greedy(num_predict=16).with_(stop=[stop]), SamplingOptions.greedy(num_predict=16),
+            SamplingOptions.greedy(num_predict=16)]
+    res = eng.generate(prompts, opts, on_text=on_text,
+                       on_token=lambda i, t: not (i == 2 and t == want[2][4]))
+    assert res[0].token_ids == want[0][:7] and res[0].text == text0[:at] == shown[0] and res[0].stats.done_reason == "stop"
+    assert res[1].token_ids == want[1] and res[1].stats.done_reason == "length" and shown[1] == tok.decode(want[1])
+    cut = want[2].index(want[2][4]) + 1
+    assert res[2].stats.done_reason == "abort" and res[2].token_ids[:cut] == want[2][:cut] and len(res[2].token_ids) <= cut + 1
+    eng.runner.cache.check_invariants()
+    assert eng.runner.cache.free_pages() == eng.runner.cache.num_pages and eng.runner.cache.free_slots() == 3
+
+
 def test_first_tokens_of_a_sequence(tiny_dirs):
     """Positions 0, 1, 2 one by one (a one-token prompt, then single tokens) in both dtypes."""
     from hfee_b200 import EngineConfig, ModelRunner, StepEntry

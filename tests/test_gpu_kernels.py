@@ -172,6 +172,23 @@ def test_gemm_stream(ops, m, n, k):
     _close(acc, base.double() + ref, 1e-5)
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 64])
+def test_the_head_of_the_benchmark_model(ops, m):
+    """The product the benchmark's logits come from: 128,256 rows of 2,048 for 1, 8, 16 and 64 tokens,
+    through whatever kernel ``ops.linear`` picks for that many tokens (16,032 row tiles of 8)."""
+    g = torch.Generator().manual_seed(60 + m)
+    a = torch.randn(m, 2048, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(128256, 2048, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = a.double() @ w.double().t()
+    out = torch.full((m, 128256), float("nan"), dtype=torch.float32, device=DEV)
+    ops.linear(a, w, out)
+    ops.check_status()
+    _close(out, ref, 1e-5)
+    direct = torch.full((m, 128256), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_stream(a, w, direct)                  # the streaming kernel itself takes up to 64 tokens
+    _close(direct, ref, 1e-5)
+
+
 @pytest.mark.parametrize("m", [1, 8, 9, 16, 20, 64])
 @pytest.mark.parametrize("inner,k", [(4, 8), (172, 64), (1000, 96), (8192, 256), (1028, 2048), (10004, 4104)])
 def test_gemm_stream_swiglu(ops, m, inner, k):

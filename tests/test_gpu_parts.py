@@ -215,7 +215,7 @@ def _register_toy():
             names = {"ffn.gate": p + "gate", "ffn.up": p + "up", "ffn.down": p + "down",
                      "mixer_norm.weight": p + "n1", "ffn_norm.weight": p + "n2"}
             names.update({f"mixer.{k}": p + k for k in mixer_names})
-            return LayerSpec(block=block, mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm, names=names)
+            return LayerSpec.pre_norm(block, mixer, ffn, norm, norm, names=names)
 
         local = attn.replace(window=c.window, position=PartSpec("none"))
         layers = (layer(0, attn, "qkvo"), layer(1, mean, "w"), layer(2, attn, "qkvo"), layer(3, local, "qkvo"))
@@ -284,17 +284,26 @@ def test_toy_architecture_with_state_runs_through_the_engine(tmp_path, dtype):
     seqs = [rng.integers(0, 211, size=n).tolist() for n in (50, 9, 33, 70)]
     refs = [toy_plain_forward(w, s, dtype == "bfloat16") for s in seqs]
     e = EngineConfig(dtype=dtype, page_size=16, max_requests=3, max_context=128, max_cache_tokens=10 * 16,
-                     max_batch_tokens=96, use_cuda_graphs=False)
+                     max_batch_tokens=96)                   # CUDA graphs stay at their default: on
     runner = ModelRunner(d, e)
+    # the toy mixer walks the step's host-side list of requests, so it does not declare itself safe
+    # to capture, and a model with such a part never replays a graph
+    assert not runner.model.graph_safe
     needs = runner.model.cache_needs()
     assert needs[0] == PagedKV(1, 32, None) and needs[1] == needs[2] == FixedState((80,), "float32")
     assert needs[3] == PagedKV(1, 32, 21)
     assert len(runner.cache.paged) == 2 and len(runner.cache.states) == 1
     windowed = [g for g in runner.cache.paged if g.need.window][0]
-    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(7, 2, 16, 3, 2, 33)), ru.mixed(seqs, live=3, seed=1)):
+    # the last scheme: decode-only steps of equal batch size while slots and positions change
+    # (requests leave after 5 to 40 tokens, the fourth joins in a freed slot): a slot id or a
+    # position frozen into a replayed graph would show here
+    together = ru.batched_decode(seqs, tails=[40, 5, 30, 35], live=3)
+    assert sum(all(len(t) == 1 for _, t, _ in st["entries"]) for st in together) >= 30
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(7, 2, 16, 3, 2, 33)), ru.mixed(seqs, live=3, seed=1), together):
         got = ru.run_in_process(runner, steps)
         for i in range(len(seqs)):
             assert ru.rel_err(got[i], refs[i]) < TOL[dtype], f"request {i}"
+    assert runner.graph_replays == 0
     # the windowed group gave pages back while requests were still running: a request of 70 tokens
     # never held more than ceil((21 + longest portion) / 16) + 1 of them
     s = runner.open()
@@ -383,8 +392,7 @@ def _register_routed_toy():
             names = {"mixer.q": p + "q", "mixer.k": p + "k", "mixer.v": p + "v", "mixer.o": p + "o",
                      "mixer_norm.weight": p + "n1", "ffn_norm.weight": p + "n2"}
             names.update({"ffn." + k: p + "ffn_" + k for k in (("router", "gate", "up", "down") if i % 2 else ("gate", "up", "down"))})
-            layers.append(LayerSpec(block=PartSpec("pre_norm", width=w), mixer=attn, feed_forward=ffn, mixer_norm=norm,
-                                    ffn_norm=norm, names=names))
+            layers.append(LayerSpec.pre_norm(PartSpec("pre_norm", width=w), attn, ffn, norm, norm, names=names))
         return ModelSpec(width=w, vocab=d["vocab_size"], embedding=PartSpec("token", vocab=d["vocab_size"], width=w),
                          layers=tuple(layers), schedule=ModelSpec.sequential(len(layers)), final_norm=norm,
                          head=PartSpec("linear", vocab=d["vocab_size"], width=w, tied=False),
@@ -439,8 +447,150 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     seqs = [rng.integers(0, 97, size=n).tolist() for n in (45, 12, 30)]
     refs = [routed_plain_forward(w, s) for s in seqs]
     runner = ModelRunner(d, EngineConfig(dtype="float32", page_size=16, max_requests=3, max_context=64,
-                                         max_cache_tokens=7 * 16, max_batch_tokens=64, use_cuda_graphs=False))
-    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(5, 2, 9, 2, 20)), ru.mixed(seqs, live=3, seed=2)):
+                                         max_cache_tokens=7 * 16, max_batch_tokens=64))
+    assert not runner.model.graph_safe            # the routed feed-forward picks its rows on the host
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(5, 2, 9, 2, 20)), ru.mixed(seqs, live=3, seed=2),
+                  ru.batched_decode(seqs, tails=[33, 6, 20])):
         got = ru.run_in_process(runner, steps)
         for i in range(len(seqs)):
             assert ru.rel_err(got[i], refs[i]) < 1e-4, f"request {i}"
+
+
+# ---------------------------------------------------------------------------------------------
+# A third toy architecture: other arrangements of the same parts.  A block with a norm in front of
+# and behind each of its two branches (four norms), and a block without a feed-forward; both are
+# block parts defined and registered here, the layers name their parts as data.
+
+def _register_sandwich_toy():
+    from hfee_b200 import LayerSpec, ModelSpec, PartSpec, register_architecture, register_part
+    from hfee_b200.parts import Block, part_class
+
+    class SandwichBlock(Block):
+        """``x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x)))``.  Mixers and feed-forwards add
+        into the float32 buffer they are given; here that is a zeroed scratch, whose norm then joins
+        the stream."""
+        needs = ("mixer", "ffn", "pre_mixer_norm", "post_mixer_norm", "pre_ffn_norm", "post_ffn_norm")
+        graph_safe = True            # device-side work on buffers that live as long as the engine
+
+        def __init__(self, spec, tensors, rt, parts):
+            super().__init__(spec, tensors, rt, parts)
+            self.width = int(spec.width)
+
+        def _branch(self, pre, part, post, residual, step, *more):
+            rt, n = self.rt, step.n
+            xn = rt.scratch("sandwich_in", (rt.max_tokens, self.width))[:n]
+            branch = rt.scratch("sandwich_branch", (rt.max_tokens, self.width), torch.float32)[:n]
+            normed = rt.scratch("sandwich_out", (rt.max_tokens, self.width), torch.float32)[:n]
+            pre.forward(residual, xn)
+            branch.zero_()
+            part.forward(xn, branch, step, *more)
+            post.forward(branch, normed)
+            residual += normed
+
+        def forward(self, residual, step, cache, writes_cache):
+            p = self.parts
+            self._branch(p["pre_mixer_norm"], p["mixer"], p["post_mixer_norm"], residual, step, cache, writes_cache)
+            self._branch(p["pre_ffn_norm"], p["ffn"], p["post_ffn_norm"], residual, step)
+
+    class MixerOnlyBlock(Block):
+        """``x += mixer(norm(x))``: a layer without a feed-forward."""
+        needs = ("mixer", "norm")
+        graph_safe = True
+
+        def forward(self, residual, step, cache, writes_cache):
+            xn = self.rt.scratch("mixer_only_in", (self.rt.max_tokens, int(self.spec.width)))[:step.n]
+            self.parts["norm"].forward(residual, xn)
+            self.parts["mixer"].forward(xn, residual, step, cache, writes_cache)
+
+    for kind, cls in (("toy_sandwich", SandwichBlock), ("toy_mixer_only", MixerOnlyBlock)):
+        try:
+            part_class("block", kind)
+        except ValueError:
+            register_part("block", kind, cls)
+
+    @dataclass(frozen=True)
+    class SandwichConfig:
+        d: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(dict(d))
+
+    def spec_of(c):
+        d = c.d
+        w = d["width"]
+        pos = PartSpec("rotary", head_dim=d["head_dim"], rope_dim=d["head_dim"], theta=5000.0, scaling=None, pairing="half")
+        attn = PartSpec("attention", width=w, heads=d["heads"], kv_heads=d["kv_heads"], head_dim=d["head_dim"],
+                        position=pos, window=None, scale=None)
+        ffn = PartSpec("swiglu", width=w, inner=d["inner"])
+        norm = PartSpec("rms_norm", width=w, eps=d["eps"])
+        layers = []
+        for i in range(d["layers"]):
+            p = f"s{i}."
+            names = {"mixer.q": p + "q", "mixer.k": p + "k", "mixer.v": p + "v", "mixer.o": p + "o"}
+            if i % 2 == 0:
+                parts = {"mixer": ("mixer", attn), "ffn": ("feed_forward", ffn)}
+                parts.update({k: ("norm", norm) for k in ("pre_mixer_norm", "post_mixer_norm", "pre_ffn_norm", "post_ffn_norm")})
+                names.update({"ffn.gate": p + "gate", "ffn.up": p + "up", "ffn.down": p + "down"})
+                names.update({k + ".weight": p + k for k in ("pre_mixer_norm", "post_mixer_norm", "pre_ffn_norm", "post_ffn_norm")})
+                layers.append(LayerSpec(PartSpec("toy_sandwich", width=w), parts, names))
+            else:
+                names["norm.weight"] = p + "norm"
+                layers.append(LayerSpec(PartSpec("toy_mixer_only", width=w), {"mixer": ("mixer", attn), "norm": ("norm", norm)}, names))
+        return ModelSpec(width=w, vocab=d["vocab_size"], embedding=PartSpec("token", vocab=d["vocab_size"], width=w),
+                         layers=tuple(layers), schedule=ModelSpec.sequential(len(layers)), final_norm=norm,
+                         head=PartSpec("linear", vocab=d["vocab_size"], width=w, tied=True),
+                         names={"embedding.table": "emb", "final_norm.weight": "norm"}, max_positions=256)
+
+    register_architecture("ToySandwichForCausalLM", SandwichConfig.from_dict, spec_of)
+
+
+SANDWICH = {"architectures": ["ToySandwichForCausalLM"], "width": 72, "heads": 6, "kv_heads": 2, "head_dim": 16,
+            "inner": 88, "layers": 3, "vocab_size": 131, "eps": 1e-5}
+
+
+def sandwich_plain_forward(w, tokens, bf16):
+    f = (lambda a: plain.to_bf16_grid(a)) if bf16 else (lambda a: a)
+    c = SANDWICH
+    n = len(tokens)
+    inv = plain.rope_inv_freq(c["head_dim"], 5000.0)
+    norm = lambda x, name: plain.rms_norm(x, w[name], c["eps"])
+
+    def attend(xb, p):
+        q = plain.rope(plain.linear(xb, f(w[p + "q"])), c["heads"], c["head_dim"], range(n), inv, "half")
+        k = plain.rope(plain.linear(xb, f(w[p + "k"])), c["kv_heads"], c["head_dim"], range(n), inv, "half")
+        att = plain.attention(q, k, plain.linear(xb, f(w[p + "v"])), c["heads"], c["kv_heads"], c["head_dim"])
+        return plain.linear(att, f(w[p + "o"]))
+
+    x = plain.embed(f(w["emb"]), tokens)
+    for i in range(c["layers"]):
+        p = f"s{i}."
+        if i % 2 == 0:
+            x = x + norm(attend(norm(x, p + "pre_mixer_norm"), p), p + "post_mixer_norm")
+            h = plain.feed_forward(norm(x, p + "pre_ffn_norm"), f(w[p + "gate"]), f(w[p + "up"]), f(w[p + "down"]))
+            x = x + norm(h, p + "post_ffn_norm")
+        else:
+            x = x + attend(norm(x, p + "norm"), p)
+    return plain.linear(norm(x, "norm"), f(w["emb"]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blocks_with_four_norms_and_without_a_feed_forward(tmp_path, dtype):
+    from hfee_b200 import EngineConfig, ModelRunner, write_random_model
+    _register_sandwich_toy()
+    d = str(tmp_path / "sandwich")
+    write_random_model(d, SANDWICH, seed=8, dtype="float32", std=0.08)
+    w = plain.read_safetensors(d + "/model.safetensors")
+    assert "s0.post_ffn_norm" in w and "s1.norm" in w and "s1.gate" not in w       # the layers' parts decide the tensors
+    rng = np.random.default_rng(3)
+    seqs = [rng.integers(0, 131, size=n).tolist() for n in (47, 11, 60, 35)]
+    refs = [sandwich_plain_forward(w, s, dtype == "bfloat16") for s in seqs]
+    runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=16, max_requests=3, max_context=64,
+                                         max_cache_tokens=8 * 16, max_batch_tokens=64))
+    assert runner.model.graph_safe
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(5, 2, 9, 2, 20)), ru.mixed(seqs, live=3, seed=4),
+                  ru.batched_decode(seqs, tails=[34, 6, 30, 25], live=3)):
+        got = ru.run_in_process(runner, steps)
+        for i in range(len(seqs)):
+            assert ru.rel_err(got[i], refs[i]) < TOL[dtype], f"request {i}"
+    assert runner.graph_replays > 10          # decode-only steps of these blocks replay from CUDA graphs
