@@ -79,8 +79,11 @@ def test_many_requests_decoding_together(model, crowd, live, dtype, tol):
     d, cfg, _, _ = model
     heads, full, full_refs = crowd
     tails = _tails(live)
-    seqs = [full[i][:heads[i] + tails[i]] for i in range(live)]       # a prefix of a sequence has the same logits
-    refs = [full_refs[i][:len(seqs[i])] for i in range(live)]
+    pick = range(64 - live, 64)                                        # the longest ones
+    heads = [heads[i] for i in pick]
+    seqs = [full[i][:h + t] for i, h, t in zip(pick, heads, tails)]    # a prefix of a sequence has the same logits
+    assert all(len(s) == h + t for s, h, t in zip(seqs, heads, tails))
+    refs = [full_refs[i][:len(s)] for i, s in zip(pick, seqs)]
     e = EngineConfig(dtype=dtype, page_size=64, max_requests=live, max_context=4096, max_cache_tokens=live * 256,
                      max_batch_tokens=512, use_cuda_graphs=True)
     runner = ModelRunner(d, e)

@@ -586,7 +586,7 @@ def test_blocks_with_four_norms_and_without_a_feed_forward(tmp_path, dtype):
     seqs = [rng.integers(0, 131, size=n).tolist() for n in (47, 11, 60, 35)]
     refs = [sandwich_plain_forward(w, s, dtype == "bfloat16") for s in seqs]
     runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=16, max_requests=3, max_context=64,
-                                         max_cache_tokens=8 * 16, max_batch_tokens=64))
+                                         max_cache_tokens=11 * 16, max_batch_tokens=64))
     assert runner.model.graph_safe
     for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(5, 2, 9, 2, 20)), ru.mixed(seqs, live=3, seed=4),
                   ru.batched_decode(seqs, tails=[34, 6, 30, 25], live=3)):
