@@ -3,6 +3,7 @@
 bfloat16 weights, one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 1b|8b|13b] [--layers L] [--dtype bfloat16|float32] [--breakdown]
 
 A "step" is one decode step of a batch of 8 requests whose prompts of 2,048 tokens
 are already cached (context limit 4,096).  The JSON line carries: ``value`` (decoded
@@ -12,6 +13,12 @@ tokens a second, timed on the device over exactly K steps), ``e2e`` (the same th
 measured HBM copy bandwidth), ``points`` (decode at batch 1 and 64), ``clocks`` and
 ``gpu_launches``.  Weights (2.5 GB) and the cache of the live requests are far larger
 than the 126 MB L2, so no L2 flush is needed between steps.
+
+``--shape 8b`` / ``13b`` run the layer sizes of Llama-3.1-8B / Llama-2-13B (by default with fewer
+layers, named beside the full number in ``config``), ``--dtype float32`` the true 32-bit path.
+``--breakdown`` prints, instead of the line above, what each class of kernels costs inside the decode
+step at batch 1, 8 and 64 and inside the prompt pass: the step is timed again with that class's
+launches left out (results wrong, timing not), and the difference is the class's cost in place.
 """
 import argparse
 import json
@@ -34,7 +41,25 @@ MODEL = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True,
 }
-FULL_LAYERS = 16
+# BASELINE.json configs[3] and configs[4]: the Llama-3.1-8B and Llama-2-13B shapes.
+SHAPES = {
+    "1b": (MODEL, "llama-3.2-1b-shape", 16),
+    "8b": ({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+        "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": False,
+    }, "llama-3.1-8b-shape", 8),
+    "13b": ({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 40,
+        "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0,
+        "rope_scaling": None, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096, "tie_word_embeddings": False,
+    }, "llama-2-13b-shape", 8),
+}
+E2E_MIN_STEPS = 128                               # the wall-clock window of the end-to-end number never shrinks below this
 PROMPT = 2048
 CONTEXT = 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -48,7 +73,7 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             out = dict(FALLBACK_PEAKS)
-            for k in out:
+            for k in list(out) + ["sm_max_mhz"]:
                 if isinstance(d.get(k), (int, float)):
                     out[k] = float(d[k])
             out["source"] = "measured"
@@ -107,13 +132,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_numbers(cfg, layers):
+def model_numbers(cfg, layers, elem=2):
+    """Sizes a decode step reads: every matrix once (the embedding table only as the head, or the
+    head of its own), ``elem`` bytes per weight and cache element."""
     d, h, kv, hd, i, v = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
                           cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
     layer_params = d * (h + 2 * kv) * hd + h * hd * d + 3 * d * i
     return {"layer_params": layer_params, "head_params": v * d,
-            "weight_bytes": 2 * (layers * layer_params + v * d) + 4 * (2 * layers + 1) * d,
-            "kv_bytes_per_token": 2 * layers * kv * hd * 2}
+            "weight_bytes": elem * (layers * layer_params + v * d) + 4 * (2 * layers + 1) * d,
+            "kv_bytes_per_token": 2 * layers * kv * hd * elem}
 
 
 def prefill_flops(cfg, layers, t):
@@ -136,7 +163,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes, if memory or time needs it")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes: Llama-3.2-1B (the headline), 3.1-8B, 2-13B")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers of the same sizes, if memory or time needs it (config names both numbers)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--breakdown", action="store_true", help="cost of each class of kernels inside the steps, instead of the bench line")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
@@ -156,8 +187,19 @@ def main():
     from hfee_b200.kernels import ops
 
     pk = peaks()
-    cfg = dict(MODEL, num_hidden_layers=args.layers)
-    nums = model_numbers(cfg, args.layers)
+    model, model_name, default_layers = SHAPES[args.shape]
+    full_layers = model["num_hidden_layers"]
+    layers = args.layers or default_layers
+    f32 = args.dtype == "float32"
+    elem = 4 if f32 else 2
+    cfg = dict(model, num_hidden_layers=layers)
+    nums = model_numbers(cfg, layers, elem)
+    context = min(CONTEXT, cfg["max_position_embeddings"])
+    if f32:      # no tensor cores on this path: FFMA rate of this device at its highest clock
+        props = torch.cuda.get_device_properties(0)
+        compute_peak = props.multi_processor_count * 128 * 2 * (pk.get("sm_max_mhz") or 1965.0) * 1e6
+    else:
+        compute_peak = pk["bf16_tflops"] * 1e12
     rng = np.random.default_rng(0)
     tmp = tempfile.mkdtemp(prefix="hfee_bench_")
     t0 = time.time()
@@ -166,15 +208,15 @@ def main():
 
     if args.only != "all":
         args.no_points = args.no_e2e = True
-    max_b = 64 if not args.no_points else args.batch
-    engine = Engine(tmp, dtype="bfloat16", page_size=64, max_requests=max(max_b, args.batch), max_context=CONTEXT,
-                    max_batch_tokens=PROMPT, max_cache_tokens=max(max_b, args.batch) * CONTEXT,
-                    use_cuda_graphs=not args.no_graphs)
+    max_b = 64 if (args.breakdown or not args.no_points) else args.batch
+    max_b = max(max_b, args.batch)
+    engine = Engine(tmp, dtype=args.dtype, page_size=64, max_requests=max_b, max_context=context,
+                    max_batch_tokens=PROMPT, max_cache_tokens=max_b * context, use_cuda_graphs=not args.no_graphs)
     runner = engine.runner
     import shutil
     shutil.rmtree(tmp, ignore_errors=True)
     vocab = cfg["vocab_size"]
-    sample_out = torch.zeros(max(max_b, args.batch), dtype=torch.int32, device=runner.device)
+    sample_out = torch.zeros(max_b, dtype=torch.int32, device=runner.device)
     argmax_scratch = engine.sampler.argmax_scratch
 
     def timed(fn, iters):
@@ -187,7 +229,6 @@ def main():
         torch.cuda.synchronize()
         return a.elapsed_time(b)
 
-    # ---------------------------------------------------------------- prefill of 2,048 tokens
     prompt = rng.integers(0, vocab, size=PROMPT).tolist()
 
     def prefill_once(_):
@@ -195,6 +236,75 @@ def main():
         runner.step([StepEntry(s, prompt, [PROMPT - 1])])
         runner.close(s)
 
+    def decode_point(batch, steps, warmup):
+        """Time ``steps`` decode steps of ``batch`` requests with prompts of PROMPT tokens cached."""
+        slots = [runner.open() for _ in range(batch)]
+        for s in slots:
+            runner.step([StepEntry(s, rng.integers(0, vocab, size=PROMPT).tolist(), [])])
+        start = PROMPT
+        feed = rng.integers(0, vocab, size=(warmup + steps, batch)).tolist()
+
+        def one(i):
+            logits = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            ops.tag("sample")
+            ops.argmax(logits, sample_out[:batch], argmax_scratch)
+
+        for i in range(warmup):
+            one(i)
+        before = ops.launch_count()
+        print(f"[bench] timed decode (batch {batch}) starts after {before} launches", file=sys.stderr, flush=True)
+        ms = timed(lambda i: one(warmup + i), steps)
+        launches = ops.launch_count() - before
+        ctx = start + warmup + (steps - 1) / 2.0 + 1
+        for s in slots:
+            runner.close(s)
+        return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+                "bytes": nums["weight_bytes"] + batch * ctx * nums["kv_bytes_per_token"], "context": ctx}
+
+    config = {"model": model_name, "global_batch": args.batch, "seq_len": context,
+              "prompt_len": PROMPT, "parallelism": "single_gpu", "layers": layers,
+              "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+              "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+              "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_embeddings": bool(cfg["tie_word_embeddings"]),
+              "page_size": 64, "weights": "random bf16 seed 0", "l2": "inputs larger than L2",
+              "peaks": pk["source"] + (", float32 against the FFMA rate" if f32 else "")}
+
+    # ---------------------------------------------------------------- cost of each class of kernels
+    if args.breakdown:
+        per_layer = ["norm", "qkv", "rope", "attention", "o", "gate_up", "down"]
+        once = ["embed", "head", "sample"]
+        out = {"breakdown": "step time minus step time with the class left out; us per layer for layer classes, us per step for the rest",
+               "config": config, "dtype": "bf16" if not f32 else "fp32"}
+
+        def forget_graphs():
+            runner._graphs.clear()
+            runner._graph_seen.clear()
+
+        def classes_of(measure):
+            base = measure()
+            res = {"step_ms": round(base, 4)}
+            for c in per_layer + once:
+                ops.leave_out([c])
+                forget_graphs()
+                t = measure()
+                res[c] = round((base - t) * 1e3 / (layers if c in per_layer else 1), 2)
+            ops.leave_out([])
+            forget_graphs()
+            res["sum_ms"] = round(sum(res[c] * (layers if c in per_layer else 1) for c in per_layer + once) / 1e3, 4)
+            return res
+
+        clocks = ClockSampler()
+        clocks.start()
+        for b in (1, 8, 64):            # every measurement on freshly read prompts: the same context each time
+            out[f"decode_b{b}"] = classes_of(lambda: decode_point(b, 48, 4)["ms_per_step"])
+        for _ in range(args.warmup):
+            prefill_once(0)
+        out["prefill_2048"] = classes_of(lambda: timed(prefill_once, 3) / 3)
+        out["clocks"] = clocks.summary()
+        print(json.dumps(out))
+        return 0
+
+    # ---------------------------------------------------------------- prefill of 2,048 tokens
     clocks = ClockSampler()
     prefill = None
     if args.only in ("all", "prefill"):
@@ -204,9 +314,9 @@ def main():
         p_iters = 5 if args.only == "all" else 1
         print(f"[bench] timed prefill starts after {ops.launch_count()} launches", file=sys.stderr, flush=True)
         p_ms = timed(prefill_once, p_iters) / p_iters
-        p_flops = prefill_flops(cfg, args.layers, PROMPT)
+        p_flops = prefill_flops(cfg, layers, PROMPT)
         prefill = {"value": round(PROMPT / (p_ms / 1e3), 1), "tokens": PROMPT, "ms": round(p_ms, 3),
-                   "frac": round(p_flops / (p_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+                   "frac": round(p_flops / (p_ms / 1e3) / compute_peak, 4)}
     else:
         clocks.start()
     if args.only == "prefill":
@@ -214,28 +324,6 @@ def main():
         return 0
 
     # ---------------------------------------------------------------- decode
-    def decode_point(batch, steps, warmup):
-        slots = [runner.open() for _ in range(batch)]
-        for s in slots:
-            runner.step([StepEntry(s, rng.integers(0, vocab, size=PROMPT).tolist(), [])])
-        feed = rng.integers(0, vocab, size=(warmup + steps, batch)).tolist()
-
-        def one(i):
-            logits = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
-            ops.argmax(logits, sample_out[:batch], argmax_scratch)
-
-        for i in range(warmup):
-            one(i)
-        before = ops.launch_count()
-        print(f"[bench] timed decode (batch {batch}) starts after {before} launches", file=sys.stderr, flush=True)
-        ms = timed(lambda i: one(warmup + i), steps)
-        launches = ops.launch_count() - before
-        ctx = PROMPT + warmup + (steps - 1) / 2.0 + 1
-        for s in slots:
-            runner.close(s)
-        return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
-                "bytes": nums["weight_bytes"] + batch * ctx * nums["kv_bytes_per_token"], "context": ctx}
-
     main_pt = decode_point(args.batch, args.steps, args.warmup)
     clock_summary = clocks.summary()
     points = {}
@@ -247,11 +335,13 @@ def main():
     # Host tokens in, host tokens out: every step copies its token ids and positions from pinned
     # host memory and reads the sampled ids back.  Prompts are read first; the timed window opens
     # when every request has produced `warmup` tokens (all are decoding by then) and closes when
-    # the first one ends, so it holds decode steps of the full batch only.
+    # the first one ends, so it holds decode steps of the full batch only.  It is a wall-clock
+    # window, so it never holds fewer than E2E_MIN_STEPS steps, whatever --steps is.
     e2e = None
     if not args.no_e2e:
+        e2e_steps = max(args.steps, E2E_MIN_STEPS)
         prompts = [rng.integers(0, vocab, size=PROMPT).tolist() for _ in range(args.batch)]
-        opts = SamplingOptions.greedy(num_predict=args.warmup + args.steps)
+        opts = SamplingOptions.greedy(num_predict=args.warmup + e2e_steps)
         counts = [0] * args.batch
         marks = {}
 
@@ -259,7 +349,7 @@ def main():
             counts[i] += 1
             if "start" not in marks and min(counts) >= args.warmup:
                 marks["start"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
-            if "start" in marks and "end" not in marks and max(counts) >= args.warmup + args.steps:
+            if "start" in marks and "end" not in marks and max(counts) >= args.warmup + e2e_steps:
                 marks["end"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
 
         engine.generate(prompts, opts, on_token=on_token)
@@ -270,19 +360,19 @@ def main():
                "d2h_bytes_per_step": round((d1 - d0) / n_steps, 1), "steps": n_steps}
 
     achieved = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
+    # The reference publishes one figure: "about 7" tokens/s for one conversation with llama3.2:1b (a
+    # 2-core CPU, quantised weights).  The like-for-like point here is decode at batch 1 of the 1B shape.
+    single = points.get("decode_b1") if args.shape == "1b" and not f32 else None
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape)", "value": round(main_pt["tok_s"], 1),
+        "metric": f"decode tok/s at batch {args.batch} ({model_name.replace('-shape', '').replace('llama', 'Llama')} shape)",
+        "value": round(main_pt["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_pt["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(main_pt["tok_s"] / PUBLISHED_TOK_S, 1), "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": round(single / PUBLISHED_TOK_S, 1) if single else None,
+        "vs_baseline_of": "decode_b1 over the reference's published single-conversation rate (CPU, quantised weights)",
+        "dtype": "fp32" if f32 else "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "llama-3.2-1b-shape", "global_batch": args.batch, "seq_len": CONTEXT,
-                   "prompt_len": PROMPT, "parallelism": "single_gpu", "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_embeddings": True,
-                   "page_size": 64, "weights": "random bf16 seed 0", "l2": "inputs larger than L2",
-                   "peaks": pk["source"]},
+        "config": config,
         "e2e": e2e,
         "gpu_launches": int(main_pt["launches"]),
         "prefill": prefill,

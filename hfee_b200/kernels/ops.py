@@ -94,6 +94,40 @@ def loaded_library_path() -> Optional[str]:
 
 _LAUNCHES = 0
 
+# Measuring what a class of kernels costs inside a step: the parts name the class of their next
+# launches with tag(); leave_out(classes) makes every launch of those classes a no-op (the results
+# are then wrong, the timing of the rest is not), and the difference of the step time with and
+# without a class is what it costs in place, overlap with its neighbours included.
+_TAG = ""
+_LEFT_OUT: frozenset = frozenset()
+
+
+def tag(name: str) -> str:
+    """Name the class of the launches that follow; returns the class named before."""
+    global _TAG
+    before, _TAG = _TAG, name
+    return before
+
+
+def leave_out(classes=()) -> None:
+    global _LEFT_OUT
+    _LEFT_OUT = frozenset(classes)
+
+
+def _measurable(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def call(*args, **kwargs):
+        if _LEFT_OUT and _TAG in _LEFT_OUT:
+            # a product left out still lets the norm in front of it run, unless the kernel would have
+            # computed that norm itself
+            if args and not isinstance(args[0], torch.Tensor) and hasattr(args[0], "tensor") and not _norm_fusable(args[0], args[1]):
+                args[0].tensor()
+            return None
+        return fn(*args, **kwargs)
+    return call
+
 
 def launch_count() -> int:
     """Kernels launched through this module so far (a graph replay counts its kernels)."""
@@ -668,3 +702,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
     _check(lib.hfee_argmax(logits.data_ptr(), _rows(logits, "logits"), m, v, ARGMAX_CHUNKS, scratch.data_ptr(),
                            out.data_ptr(), _ptr(slots), _ptr(feedback), _stream()), lib)
     count_launches(1)
+
+
+# the entry points the parts and the sampler launch through can be left out by class (see tag())
+for _name in ("embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu",
+              "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
+    globals()[_name] = _measurable(globals()[_name])
+del _name

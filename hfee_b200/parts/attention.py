@@ -63,28 +63,35 @@ class PagedAttention(Mixer):
         q = rt.scratch("attn_q", (rt.max_tokens, self.q_cols))[:n]
         if writes_cache:
             qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n]
+            ops.tag("qkv")
             ops.linear_normed(xn, self.w_qkv, qkv)
             k_pool, v_pool = cache.k, cache.v
         else:       # reads the cache another run filled: only the queries are needed
             qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n, :self.q_cols]
+            ops.tag("qkv")
             ops.linear_normed(xn, self.w_qkv[:self.q_cols], qkv)
             k_pool = v_pool = None
         att = rt.scratch("attn_out", (rt.max_tokens, self.q_cols))[:n]
         if ops.decode_rope_fusable(step, qkv.dtype, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
                                    qkv, self.split_scratch):
             # a decode step: rotation and cache write happen inside the attention kernel
+            ops.tag("attention")
             ops.paged_attention_rope(qkv, cs, self.position.rope_dim, self.position.interleaved, writes_cache,
                                      cache.k, cache.v, cache.block_table, cache.page_size, att, self.heads,
                                      self.kv_heads, self.head_dim, self.scale, int(self.window or 0), step,
                                      self.split_scratch)
+            ops.tag("o")
             ops.linear(att, self.w_o, residual, accumulate=True)
             return
+        ops.tag("rope")
         ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
                              cache.page_size, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
                              self.position.interleaved)
+        ops.tag("attention")
         ops.paged_attention(q, cache.k, cache.v, cache.block_table, cache.page_size, step.positions,
                             step.slot_of_token, att, self.heads, self.kv_heads, self.head_dim, self.scale,
                             int(self.window or 0), step=step, scratch=self.split_scratch)
+        ops.tag("o")
         ops.linear(att, self.w_o, residual, accumulate=True)
 
 

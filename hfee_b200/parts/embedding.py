@@ -26,6 +26,7 @@ class TokenEmbedding(Part):
         self.table = tensors["table"]
 
     def forward(self, step: Any, residual: torch.Tensor) -> None:
+        ops.tag("embed")
         ops.embed(self.table, step.token_ids, residual, step.slot_of_token, getattr(step, "feedback", None))
 
 
@@ -56,8 +57,10 @@ class LinearHead(Part):
 
     def forward(self, xn, logits: torch.Tensor) -> None:
         if isinstance(xn, torch.Tensor):
+            ops.tag("head")
             ops.linear(xn, self.weight, logits)
         else:
+            ops.tag("head")
             ops.linear_normed(xn, self.weight, logits)
 
 

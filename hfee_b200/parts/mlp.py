@@ -43,7 +43,9 @@ class SwiGLUFeedForward(Part):
         n, rt = step.n, self.rt
         gu = rt.scratch("ffn_gate_up", (rt.max_tokens, 2 * self.inner))[:n]
         h = rt.scratch("ffn_hidden", (rt.max_tokens, self.inner))[:n]
+        ops.tag("gate_up")
         ops.linear_swiglu_normed(xn, self.w_gate_up, h, self.granule, gu)
+        ops.tag("down")
         ops.linear(h, self.w_down, residual, accumulate=True)
 
 

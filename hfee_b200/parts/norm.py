@@ -29,7 +29,9 @@ class RMSNorm(Part):
         self.add_unit = bool(spec.get("add_unit", False))
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        before = ops.tag("norm")
         ops.rmsnorm(x, self.weight, out, self.eps, rows=rows, add_unit=self.add_unit)
+        ops.tag(before)
 
 
     def fused_params(self):

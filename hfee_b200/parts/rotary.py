@@ -49,6 +49,7 @@ class Rotary(Part):
         t = step.memo.get(self._key)
         if t is None:
             t = self._table[:step.n]
+            ops.tag("rope")
             ops.rope_table(step.positions, self.inv_freq, t)
             step.memo[self._key] = t
         return t
