@@ -236,7 +236,7 @@ def main():
         runner.step([StepEntry(s, prompt, [PROMPT - 1])])
         runner.close(s)
 
-    def decode_point(batch, steps, warmup):
+    def decode_point(batch, steps, warmup, quiet=False):
         """Time ``steps`` decode steps of ``batch`` requests with prompts of PROMPT tokens cached."""
         slots = [runner.open() for _ in range(batch)]
         for s in slots:
@@ -252,7 +252,8 @@ def main():
         for i in range(warmup):
             one(i)
         before = ops.launch_count()
-        print(f"[bench] timed decode (batch {batch}) starts after {before} launches", file=sys.stderr, flush=True)
+        if not quiet:
+            print(f"[bench] timed decode (batch {batch}) starts after {before} launches", file=sys.stderr, flush=True)
         ms = timed(lambda i: one(warmup + i), steps)
         launches = ops.launch_count() - before
         ctx = start + warmup + (steps - 1) / 2.0 + 1
@@ -280,23 +281,34 @@ def main():
             runner._graphs.clear()
             runner._graph_seen.clear()
 
-        def classes_of(measure):
-            base = measure()
-            res = {"step_ms": round(base, 4)}
+        def classes_of(measure, rounds=3):
+            """Whole step and step without a class in turn, ``rounds`` times, medians of both: clocks move
+            under the power cap during a run this long, and neighbours in time see the same clocks."""
+            whole_all = []
+            res = {}
             for c in per_layer + once:
-                ops.leave_out([c])
-                forget_graphs()
-                t = measure()
-                res[c] = round((base - t) * 1e3 / (layers if c in per_layer else 1), 2)
+                whole, without = [], []
+                for _ in range(rounds):
+                    ops.leave_out([])
+                    forget_graphs()
+                    whole.append(measure())
+                    ops.leave_out([c])
+                    forget_graphs()
+                    without.append(measure())
+                whole_all += whole
+                res[c] = round((statistics.median(whole) - statistics.median(without)) * 1e3 /
+                               (layers if c in per_layer else 1), 2)
             ops.leave_out([])
             forget_graphs()
+            res["step_ms"] = round(statistics.median(whole_all), 4)
+            res["step_ms_spread"] = round(max(whole_all) - min(whole_all), 4)
             res["sum_ms"] = round(sum(res[c] * (layers if c in per_layer else 1) for c in per_layer + once) / 1e3, 4)
             return res
 
         clocks = ClockSampler()
         clocks.start()
         for b in (1, 8, 64):            # every measurement on freshly read prompts: the same context each time
-            out[f"decode_b{b}"] = classes_of(lambda: decode_point(b, 48, 4)["ms_per_step"])
+            out[f"decode_b{b}"] = classes_of(lambda: decode_point(b, 64, 4, quiet=True)["ms_per_step"])
         for _ in range(args.warmup):
             prefill_once(0)
         out["prefill_2048"] = classes_of(lambda: timed(prefill_once, 3) / 3)
@@ -340,16 +352,17 @@ def main():
     e2e = None
     if not args.no_e2e:
         e2e_steps = max(args.steps, E2E_MIN_STEPS)
+        e2e_warm = max(args.warmup, 8)         # the decode step's CUDA graph is captured in the first few steps
         prompts = [rng.integers(0, vocab, size=PROMPT).tolist() for _ in range(args.batch)]
-        opts = SamplingOptions.greedy(num_predict=args.warmup + e2e_steps)
+        opts = SamplingOptions.greedy(num_predict=e2e_warm + e2e_steps)
         counts = [0] * args.batch
         marks = {}
 
         def on_token(i, tok):
             counts[i] += 1
-            if "start" not in marks and min(counts) >= args.warmup:
+            if "start" not in marks and min(counts) >= e2e_warm:
                 marks["start"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
-            if "start" in marks and "end" not in marks and max(counts) >= args.warmup + e2e_steps:
+            if "start" in marks and "end" not in marks and max(counts) >= e2e_warm + e2e_steps:
                 marks["end"] = (time.perf_counter(), sum(counts), engine.h2d_bytes, engine.d2h_bytes, runner.steps_run)
 
         engine.generate(prompts, opts, on_token=on_token)

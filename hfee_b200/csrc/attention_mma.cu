@@ -165,7 +165,12 @@ attention_mma_kernel(AttnParams p) {
   // key blocks of this CTA
   int b_lo = key_lo / BLOCK_N, b_hi = pos_last / BLOCK_N;
   if (p.num_splits > 1) {
-    int per = (b_hi - b_lo + 1 + p.num_splits - 1) / p.num_splits;
+    // The launch (and a captured graph) fixes the number of splits for the longest context the
+    // engine allows; a shorter context uses only as many of them as leave each at least two key
+    // blocks, the rest find an empty range and write an empty partial result.
+    const int blocks = b_hi - b_lo + 1;
+    const int used = max(1, min(p.num_splits, blocks / 2));
+    const int per = (blocks + used - 1) / used;
     b_lo = b_lo + split * per;
     b_hi = min(b_hi, b_lo + per - 1);
   }
@@ -513,6 +518,10 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
   int token = pair / heads, head = pair % heads;
   long long base = (long long)pair * num_splits;
   float2 ml = lane < num_splits ? *reinterpret_cast<const float2*>(part_ml + (base + lane) * 2) : make_float2(-INFINITY, 0.f);
+  // splits that found no keys (a context shorter than the launch was planned for) hold (-inf, 0) and
+  // no output; they come last, so only the leading ones are read
+  const unsigned live = __ballot_sync(0xffffffffu, ml.x != -INFINITY);
+  num_splits = live ? 32 - __clz(live) : 0;
   float w = 0.f, inv = 0.f;
   bool have_w = false;
   for (int d0 = 0; d0 < hd; d0 += 128) {         // every lane takes every trip: the shuffles need the whole warp
