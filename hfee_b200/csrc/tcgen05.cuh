@@ -54,13 +54,16 @@ __device__ __forceinline__ uint64_t global_ns() {
 // so waiting warps do not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;        // a phase that is already complete costs least this way
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
+  uint64_t t0 = 0;
 #pragma unroll 1
-  for (;;) {
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_ns() - t0 > WAIT_NS) break;
+    if ((i & 31u) == 31u) {                       // the timer is slow to read: look at it now and then only
+      if (*abort_flag) return false;
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_NS) break;
+    }
   }
   *abort_flag = 1;
   return false;
