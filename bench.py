@@ -272,8 +272,7 @@ def main():
 
     # ---------------------------------------------------------------- cost of each class of kernels
     if args.breakdown:
-        # "tail": output projection, norm and feed-forward of a decode step of at most 8 tokens as one kernel
-        per_layer = ["norm", "qkv", "rope", "attention", "o", "gate_up", "down", "tail"]
+        per_layer = ["norm", "qkv", "rope", "attention", "o", "gate_up", "down"]
         once = ["embed", "head", "sample"]
         out = {"breakdown": "step time minus step time with the class left out; us per layer for layer classes, us per step for the rest",
                "config": config, "dtype": "bf16" if not f32 else "fp32"}

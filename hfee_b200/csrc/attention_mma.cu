@@ -12,7 +12,6 @@
 // combine kernel merges them in split order.
 // Reference: hostfog/hfee internal/llm/forward.go:146-178, internal/ggml/ops.go:136-150.
 #include "common.cuh"
-#include <stdlib.h>
 
 #ifndef HFEE_ATTN_EXPORT
 #define HFEE_ATTN_EXPORT 1
@@ -583,8 +582,7 @@ int dispatch_mode(const AttnParams& p, bool ksplit, int q_tiles, int kv_heads, i
   // shared-memory footprint (fewer CTAs per SM) does not add a wave; otherwise two
   constexpr int DEEP = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
   long long ctas = (long long)p.num_splits * kv_heads * requests;
-  static const bool shallow = getenv("HFEE_ATTN_SHALLOW") != nullptr;
-  if (!shallow && DEEP > 2 && ctas <= 3 * hfee_sm_count()) return launch<HD, true, DEEP>(p, q_tiles, kv_heads, requests, stream);
+  if (DEEP > 2 && ctas <= 3 * hfee_sm_count()) return launch<HD, true, DEEP>(p, q_tiles, kv_heads, requests, stream);
   return launch<HD, true, 2>(p, q_tiles, kv_heads, requests, stream);
 }
 

@@ -6,7 +6,6 @@ where that matters, and prints what it achieved against the roofline that bounds
     python -m hfee_b200.kernels.microbench gemm_skinny  --m 64 --n 2048 --k 8192 --epilogue accum
     python -m hfee_b200.kernels.microbench attention_decode  --batch 8 --context 2048 --heads 32 --kv-heads 8 --head-dim 64
     python -m hfee_b200.kernels.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
-    python -m hfee_b200.kernels.microbench decode_tail --m 8 --k 2048 --n 8192 --graph     (width --k, inner --n)
 
 ``--iters`` timed launches follow ``--warmup`` untimed ones; ``--rotate`` distinct weight
 buffers are cycled so that a weight-streaming kernel never finds its weights in L2.  The
@@ -81,37 +80,6 @@ def _gemm(args, kind: str) -> dict:
             "tflops": round(flops / sec / 1e12, 1), "gbs": round(bytes_ / sec / 1e9, 1)}
 
 
-def _decode_tail(args) -> dict:
-    """The fused tail of a layer against the separate kernels, weights rotated so that none is found in L2."""
-    m, d, q, i = args.m, args.k, args.k, args.n
-    g = lambda *s: (torch.randn(*s, device=DEV) * 0.05).to(torch.bfloat16)
-    sets = [(g(d, q), g(2 * i, d), g(d, i)) for _ in range(args.rotate)]
-    att, residual = g(m, q), torch.randn(m, d, device=DEV)
-    norm_w = torch.ones(d, device=DEV)
-    hidden = torch.empty(m, i, dtype=torch.bfloat16, device=DEV)
-    xn = torch.empty(m, d, dtype=torch.bfloat16, device=DEV)
-    gu = torch.empty(m, 2 * i, dtype=torch.bfloat16, device=DEV)
-
-    def fused(j):
-        w_o, w_gu, w_down = sets[j % len(sets)]
-        ops.decode_tail(att, w_o, residual, norm_w, 1e-5, False, w_gu, w_down, hidden)
-
-    def separate(j):
-        w_o, w_gu, w_down = sets[j % len(sets)]
-        ops.linear(att, w_o, residual, accumulate=True)
-        ops.rmsnorm(residual, norm_w, xn, 1e-5)
-        ops.linear_swiglu(xn, w_gu, hidden, 4, gu)
-        ops.linear(hidden, w_down, residual, accumulate=True)
-
-    t_fused = _time(fused, args.warmup, args.iters)
-    t_sep = _time(separate, args.warmup, args.iters)
-    ops.check_status()
-    bytes_ = 2.0 * (d * q + 3 * d * i)
-    return {"kernel": "decode_tail", "m": m, "width": d, "inner": i, "us": round(t_fused * 1e6, 2),
-            "gbs": round(bytes_ / t_fused / 1e9, 1), "separate_us": round(t_sep * 1e6, 2),
-            "separate_gbs": round(bytes_ / t_sep / 1e9, 1)}
-
-
 class _Batch:
     pass
 
@@ -156,8 +124,7 @@ def _attention(args, decode: bool) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "attention_decode", "attention_prefill",
-                                       "decode_tail"])
+    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "attention_decode", "attention_prefill"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -183,9 +150,7 @@ def main(argv=None) -> int:
     GRAPH = args.graph
     ops.USE_TC_ATTENTION = args.tc_attention or not args.no_tc_attention
     torch.manual_seed(0)
-    if args.kernel == "decode_tail":
-        res = _decode_tail(args)
-    elif args.kernel.startswith("gemm"):
+    if args.kernel.startswith("gemm"):
         res = _gemm(args, args.kernel)
     else:
         res = _attention(args, args.kernel == "attention_decode")

@@ -6,7 +6,6 @@ CUDA device of compute capability 10.x and the built library they raise.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -38,8 +37,6 @@ _SIGNATURES = {
     "hfee_gemm_tcgen05_stream_k": [_I, _I, _I, _I, _L],
     "hfee_gemm_skinny": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _P],
     "hfee_gemm_skinny_splits": [_I, _I, _I, _L],
-    "hfee_decode_tail": [_P, _L, _P, _L, _P, _L, _P, _F, _I, _P, _L, _P, _L, _P, _L, _P, _L, _P, _I, _I, _I, _I, _P, _P, _P],
-    "hfee_decode_tail_supports": [_I, _I, _I, _I],
     "hfee_attention_tc": [_P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "hfee_attention_tc_supports": [_I, _I, _I, _I],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
@@ -69,7 +66,6 @@ def library() -> ctypes.CDLL:
     lib.hfee_sm_count.restype = _I
     lib.hfee_gemm_skinny_splits.restype = _I
     lib.hfee_attention_tc_supports.restype = _I
-    lib.hfee_decode_tail_supports.restype = _I
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -466,47 +462,6 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
 
 SWIGLU_GRANULE = 4
 
-# The tail of a layer (output projection, norm, gated feed-forward) of a decode step of at most 8
-# tokens as one persistent kernel whose weight stream runs on across its phases.
-FUSE_DECODE_TAIL = os.environ.get("HFEE_NO_DECODE_TAIL") is None
-DECODE_TAIL_MIN_TOKENS = int(os.environ.get("HFEE_DECODE_TAIL_MIN", "3"))
-DECODE_TAIL_MAX_TOKENS = 8
-_TAIL_SYNC: Optional[torch.Tensor] = None
-_TAIL_SCRATCH: dict = {}
-
-
-def decode_tail_takes(m: int, width: int, q_cols: int, inner: int, dtype: torch.dtype) -> bool:
-    return (FUSE_DECODE_TAIL and dtype == torch.bfloat16 and 1 <= m <= DECODE_TAIL_MAX_TOKENS
-            and bool(library().hfee_decode_tail_supports(m, width, q_cols, inner)))
-
-
-def decode_tail(att: torch.Tensor, w_o: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                add_unit: bool, w_gate_up: torch.Tensor, w_down: torch.Tensor, hidden: torch.Tensor) -> None:
-    """residual += att @ w_o.T; hidden = swiglu(rmsnorm(residual) @ w_gate_up.T); residual += hidden @ w_down.T
-    for at most 8 rows, in one kernel.  ``w_gate_up`` holds 4 gate rows, 4 up rows, 4 gate rows, ...;
-    ``hidden`` [m, inner] is scratch."""
-    global _TAIL_SYNC
-    lib = library()
-    m, q_cols = att.shape
-    width, inner = w_o.shape[0], w_down.shape[1]
-    assert att.dtype == w_o.dtype == w_gate_up.dtype == w_down.dtype == hidden.dtype == torch.bfloat16
-    assert residual.dtype == torch.float32 and norm_weight.dtype == torch.float32
-    assert tuple(residual.shape) == (m, width) and tuple(w_gate_up.shape) == (2 * inner, width)
-    assert tuple(w_down.shape) == (width, inner) and w_o.shape[1] == q_cols and hidden.shape[0] >= m
-    if _TAIL_SYNC is None:
-        _TAIL_SYNC = torch.zeros(2, dtype=torch.int32, device=att.device)       # the kernel leaves them zero
-    scratch = _TAIL_SCRATCH.get(width)
-    if scratch is None:       # the norm's intermediate values: x * w per column, and every CTA's share of sum x^2
-        scratch = _TAIL_SCRATCH[width] = (torch.zeros(DECODE_TAIL_MAX_TOKENS, width, dtype=torch.bfloat16, device=att.device),
-                                          torch.zeros(sm_count(), DECODE_TAIL_MAX_TOKENS, dtype=torch.float32, device=att.device))
-    y, ssq = scratch
-    _check(lib.hfee_decode_tail(att.data_ptr(), _rows(att, "att"), w_o.data_ptr(), _rows(w_o, "w_o"), residual.data_ptr(),
-                                _rows(residual, "residual"), norm_weight.data_ptr(), float(eps), int(add_unit),
-                                w_gate_up.data_ptr(), _rows(w_gate_up, "w_gate_up"), w_down.data_ptr(), _rows(w_down, "w_down"),
-                                hidden.data_ptr(), _rows(hidden, "hidden"), y.data_ptr(), _rows(y, "y"), ssq.data_ptr(),
-                                m, width, q_cols, inner,
-                                _TAIL_SYNC.data_ptr(), _status().data_ptr(), _stream()), lib)
-
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int,
                   scratch: torch.Tensor) -> None:
@@ -750,7 +705,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("decode_tail", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu",
+for _name in ("embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
     globals()[_name] = _measurable(globals()[_name])
 del _name

@@ -57,15 +57,7 @@ class PagedAttention(Mixer):
     def cache_need(self) -> PagedKV:
         return PagedKV(self.kv_heads, self.head_dim, self.window)
 
-    @property
-    def output_weight(self) -> torch.Tensor:
-        """The matrix of the mixer's last step, ``residual += heads_out @ output_weight.T``: a block that
-        can do that product together with what follows calls ``forward(..., project=False)`` and gets
-        the heads' outputs [n, heads * head_dim] back instead."""
-        return self.w_o
-
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool,
-                project: bool = True) -> Optional[torch.Tensor]:
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
         n, rt = step.n, self.rt
         cs = self.position.table(step)
         q = rt.scratch("attn_q", (rt.max_tokens, self.q_cols))[:n]
@@ -88,11 +80,9 @@ class PagedAttention(Mixer):
                                      cache.k, cache.v, cache.block_table, cache.page_size, att, self.heads,
                                      self.kv_heads, self.head_dim, self.scale, int(self.window or 0), step,
                                      self.split_scratch)
-            if not project:
-                return att
             ops.tag("o")
             ops.linear(att, self.w_o, residual, accumulate=True)
-            return None
+            return
         ops.tag("rope")
         ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
                              cache.page_size, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
@@ -101,11 +91,8 @@ class PagedAttention(Mixer):
         ops.paged_attention(q, cache.k, cache.v, cache.block_table, cache.page_size, step.positions,
                             step.slot_of_token, att, self.heads, self.kv_heads, self.head_dim, self.scale,
                             int(self.window or 0), step=step, scratch=self.split_scratch)
-        if not project:
-            return att
         ops.tag("o")
         ops.linear(att, self.w_o, residual, accumulate=True)
-        return None
 
 
 register_part("mixer", "attention", PagedAttention)

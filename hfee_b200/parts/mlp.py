@@ -39,9 +39,6 @@ class SwiGLUFeedForward(Part):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down"]
 
-    def hidden_scratch(self, n: int) -> torch.Tensor:
-        return self.rt.scratch("ffn_hidden", (self.rt.max_tokens, self.inner))[:n]
-
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any) -> None:
         n, rt = step.n, self.rt
         gu = rt.scratch("ffn_gate_up", (rt.max_tokens, 2 * self.inner))[:n]
