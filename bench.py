@@ -282,22 +282,22 @@ def main():
             runner._graph_seen.clear()
 
         def classes_of(measure, rounds=3):
-            """Whole step and step without a class in turn, ``rounds`` times, medians of both: clocks move
-            under the power cap during a run this long, and neighbours in time see the same clocks."""
+            """Whole step and step without a class back to back, ``rounds`` times; the class costs the median
+            of the differences of such pairs (the clocks move under the power cap during a run this long,
+            and the two halves of a pair see the same clocks)."""
             whole_all = []
             res = {}
             for c in per_layer + once:
-                whole, without = [], []
+                diffs = []
                 for _ in range(rounds):
                     ops.leave_out([])
                     forget_graphs()
-                    whole.append(measure())
+                    whole = measure()
                     ops.leave_out([c])
                     forget_graphs()
-                    without.append(measure())
-                whole_all += whole
-                res[c] = round((statistics.median(whole) - statistics.median(without)) * 1e3 /
-                               (layers if c in per_layer else 1), 2)
+                    diffs.append(whole - measure())
+                    whole_all.append(whole)
+                res[c] = round(statistics.median(diffs) * 1e3 / (layers if c in per_layer else 1), 2)
             ops.leave_out([])
             forget_graphs()
             res["step_ms"] = round(statistics.median(whole_all), 4)
@@ -311,7 +311,7 @@ def main():
             out[f"decode_b{b}"] = classes_of(lambda: decode_point(b, 64, 4, quiet=True)["ms_per_step"])
         for _ in range(args.warmup):
             prefill_once(0)
-        out["prefill_2048"] = classes_of(lambda: timed(prefill_once, 3) / 3)
+        out["prefill_2048"] = classes_of(lambda: timed(prefill_once, 2) / 2, rounds=7)
         out["clocks"] = clocks.summary()
         print(json.dumps(out))
         return 0
