@@ -182,6 +182,47 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   }
 }
 
+// Many rows (a prompt portion), bfloat16 out: a warp per row and the whole row in registers, so a row
+// costs one memory round trip and no block-wide barrier, and a CTA of 8 warps keeps 8 rows in flight.
+// NV float4 per lane: rows of up to 128 * NV values.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                    __nv_bfloat16* __restrict__ out, int n, int width, float eps, int add_unit) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const int src_row = rows ? rows[r] : r;                 // host-written, like the batch layout
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* xr = x + (long long)src_row * width;
+  float4 xv[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = (lane + j * 32) * 4;
+    xv[j] = c < width ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    ss = fmaf(xv[j].x, xv[j].x, ss); ss = fmaf(xv[j].y, xv[j].y, ss);
+    ss = fmaf(xv[j].z, xv[j].z, ss); ss = fmaf(xv[j].w, xv[j].w, ss);
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  const float unit = add_unit ? 1.f : 0.f;
+  __nv_bfloat16* dst = out + (long long)r * width;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = (lane + j * 32) * 4;
+    if (c >= width) continue;
+    const float4 g = __ldg(reinterpret_cast<const float4*>(w + c));
+    __nv_bfloat162 lo = __floats2bfloat162_rn(xv[j].x * scale * (g.x + unit), xv[j].y * scale * (g.y + unit));
+    __nv_bfloat162 hi = __floats2bfloat162_rn(xv[j].z * scale * (g.z + unit), xv[j].w * scale * (g.w + unit));
+    *reinterpret_cast<uint2*>(dst + c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+}
+
 HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
                           int n, int width, float eps, int add_unit, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
@@ -190,6 +231,12 @@ HFEE_API int hfee_rmsnorm(const float* x, const float* w, const int* rows, void*
   if (out_dtype == HFEE_F32) {
     if (vector) hfee_launch(rmsnorm_vec_kernel<float, 256, 4>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
     else hfee_launch(rmsnorm_kernel<float, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (float*)out, width, eps, add_unit);
+  } else if (out_dtype == HFEE_BF16 && vector && n >= 256 && width <= 128 * 32) {
+    // enough rows to fill the GPU with a warp each
+    const dim3 grid((unsigned)((n + 7) / 8));
+    if (width <= 128 * 8) hfee_launch(rmsnorm_rows_kernel<8>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, n, width, eps, add_unit);
+    else if (width <= 128 * 16) hfee_launch(rmsnorm_rows_kernel<16>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, n, width, eps, add_unit);
+    else hfee_launch(rmsnorm_rows_kernel<32>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, n, width, eps, add_unit);
   } else if (out_dtype == HFEE_BF16) {
     if (vector) hfee_launch(rmsnorm_vec_kernel<__nv_bfloat16, 256, 4>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
     else hfee_launch(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(n), dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)out, width, eps, add_unit);
