@@ -37,6 +37,8 @@ _SIGNATURES = {
     "hfee_gemm_tcgen05_stream_k": [_I, _I, _I, _I, _L],
     "hfee_gemm_skinny": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _P],
     "hfee_gemm_skinny_splits": [_I, _I, _I, _L],
+    "hfee_gemm_ring": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _P],
+    "hfee_gemm_ring_supports": [_I, _I, _I, _I],
     "hfee_attention_tc": [_P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "hfee_attention_tc_supports": [_I, _I, _I, _I],
     "hfee_attention_mma": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
@@ -281,6 +283,22 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
 _STATUS: Optional[torch.Tensor] = None
 
 
+def gemm_ring(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """out (+)= a @ w.T for at most 8 rows of ``a`` (bfloat16, width a multiple of 64): one CTA per SM
+    streams its share of the rows of ``w`` through a ring of TMA boxes.  Epilogues as in :func:`gemm_stream`."""
+    lib = library()
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
+    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    _check(lib.hfee_gemm_ring(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
+                              _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _status().data_ptr(), _stream()), lib)
+
+
+def ring_takes(m: int, n: int, k: int, epilogue: int) -> bool:
+    return bool(library().hfee_gemm_ring_supports(m, n, k, epilogue))
+
+
 def _status() -> torch.Tensor:
     global _STATUS
     if _STATUS is None:
@@ -434,12 +452,20 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         count_launches(1)
 
 
+# The ring kernel (one CTA per SM, TMA boxes) against the register-streaming one, decode step of the
+# benchmark model at batch 8: accumulating products (output and down projection) through the ring
+# 0.873 -> 0.855 ms; all products through it 0.887 ms (gate/up and qkv, whose CTAs own several row
+# tiles, are slower there); for one or two tokens the register kernel wins everywhere.
+RING_MIN_TOKENS, RING_MAX_TOKENS = 3, 8
+RING_EPILOGUES = (EPI_ACCUM,)
 STREAM_BEST_TOKENS = 16      # up to here the register-streaming kernels win; above, the skinny tcgen05 kernel
 
 
 def _small_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
     m, n = a.shape[0], w.shape[0]
-    if m <= STREAM_BEST_TOKENS or not USE_TCGEN05:
+    if _ring_rule(m, n, a.shape[1], epilogue):
+        gemm_ring(a, w, out, epilogue)
+    elif m <= STREAM_BEST_TOKENS or not USE_TCGEN05:
         gemm_stream(a, w, out, epilogue)
     elif m > 32 and 64 * 128 <= n <= 256 * 128 and a.shape[1] <= 4096 and _tensor_core_ok(a, w) and (
             epilogue != EPI_SWIGLU or out.dtype == torch.bfloat16):
@@ -448,6 +474,11 @@ def _small_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         gemm_tcgen05(a, w, out, epilogue)
     else:
         gemm_skinny(a, w, out, epilogue)
+
+
+def _ring_rule(m: int, n: int, k: int, epilogue: int) -> bool:
+    return (epilogue in RING_EPILOGUES and RING_MIN_TOKENS <= m <= RING_MAX_TOKENS and USE_TCGEN05
+            and n <= 16 * sm_count() and ring_takes(m, n, k, epilogue))
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

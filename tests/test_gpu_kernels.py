@@ -207,6 +207,61 @@ def test_gemm_stream_swiglu(ops, m, inner, k):
     _close(out, gd / (1 + torch.exp(-gd)) * ud, 6e-3)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("n,k", [(1, 64), (9, 192), (100, 576), (2048, 2048), (3072, 2048), (257, 4096), (2048, 8192),
+                                 (5000, 4160), (20004, 512)])
+def test_gemm_ring(ops, m, n, k):
+    """Fewer rows than SMs, rows that do not divide among the SMs, a K that is no multiple of a
+    stage (512), tokens that stay in shared memory (K <= 4096) and tokens that stream (above)."""
+    g = torch.Generator().manual_seed(16)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    ref = a.double() @ w.double().t()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_ring(a, w, out)
+    ops.check_status()
+    _close(out, ref, 1e-5)
+    outb = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_ring(a, w, outb)
+    _close(outb, ref, 6e-3)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_ring(a, w, acc, ops.EPI_ACCUM)
+    ops.check_status()
+    _close(acc, base.double() + ref, 1e-5)
+
+
+@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("inner,k", [(4, 64), (172, 64), (1000, 192), (8192, 2048), (1028, 4096), (10004, 4160), (300, 8192)])
+def test_gemm_ring_swiglu(ops, m, inner, k):
+    g = torch.Generator().manual_seed(17)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inner, k, generator=g) * 0.2).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([gate.reshape(inner // 4, 4, k), up.reshape(inner // 4, 4, k)], 1).reshape(2 * inner, k).contiguous().to(DEV)
+    gd, ud = a.double().cpu() @ gate.double().t(), a.double().cpu() @ up.double().t()
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_ring(a, w, out, ops.EPI_SWIGLU)
+    ops.check_status()
+    _close(out, ref, 6e-3)
+    out32 = torch.full((m, inner), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_ring(a, w, out32, ops.EPI_SWIGLU)
+    _close(out32, ref, 2e-5)
+
+
+def test_gemm_ring_refuses_what_it_cannot_do(ops):
+    from hfee_b200.kernels import KernelLibraryError
+    assert not ops.ring_takes(9, 64, 64, ops.EPI_STORE)            # more than 8 tokens
+    assert not ops.ring_takes(2, 64, 96, ops.EPI_STORE)            # K is no multiple of 64
+    assert not ops.ring_takes(2, 12, 64, ops.EPI_SWIGLU)           # SwiGLU wants groups of 8 rows
+    assert ops.ring_takes(8, 12, 64, ops.EPI_STORE)
+    a = torch.zeros(2, 96, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelLibraryError, match="multiple of 64"):
+        ops.gemm_ring(a, w, torch.empty(2, 8, dtype=torch.float32, device=DEV))
+
+
 def test_gemm_stream_refuses_unaligned(ops):
     from hfee_b200.kernels import KernelLibraryError
     a = torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV)
