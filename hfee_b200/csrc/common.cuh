@@ -43,6 +43,7 @@ extern "C" int hfee_sm_count();
 
 // 0 when the environment variable HFEE_NO_PDL is set.
 int hfee_pdl_enabled();
+int hfee_carveout();
 
 template <typename... KArgs, typename... Args>
 cudaError_t hfee_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -52,11 +53,17 @@ cudaError_t hfee_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t 
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = hfee_pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  const int carve = hfee_carveout();
+  if (carve >= 0) {
+    attr[1].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+    attr[1].val.sharedMemCarveout = (unsigned int)carve;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

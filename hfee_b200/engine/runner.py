@@ -19,6 +19,14 @@ from ..weights import Checkpoint
 from .batch import Step, StepBuffers, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+# A decode step is a chain of short kernels, and an SM changes its split between shared memory and L1
+# only when it is empty: the kernels of such a step all ask for one split (percent of the shared-memory
+# maximum).  Measured, benchmark model, ms per step against the driver's per-kernel choice: 58 % at
+# batch 2 / 4 / 8 / 16 / 32: 0.752 / 0.806 / 0.833 / 1.043 / 1.394 against 0.761 / 0.818 / 0.861 /
+# 1.064 / 1.404 (more shared memory than that starves the kernels that stream weights through L1: 100 %
+# at batch 8 takes 1.135); at batch 64, where attention is half the step and wants three CTAs of 76 KB
+# per SM, 100 % takes 1.78 against 1.85.
+DECODE_CARVEOUT_FEW, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 48
 DEVICE_TOKEN = -1        # as a single-token entry: "the token the device sampled last for this request"
 
 
@@ -92,11 +100,19 @@ class ModelRunner:
         cache.sync()
         step = Step(entries, cache.length, self.buffers)
         step.feedback = self.feedback
-        if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
-                and all(tuple(e.want) == (0,) for e in entries)):
-            logits = self._graphed_forward(step)
-        else:
-            logits = self.model.forward(step, cache.views())
+        carved = self.device.type == "cuda" and step.decode_only
+        if carved:
+            from ..kernels import ops
+            ops.set_carveout(DECODE_CARVEOUT_MANY if step.r >= DECODE_MANY_REQUESTS else DECODE_CARVEOUT_FEW)
+        try:
+            if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
+                    and all(tuple(e.want) == (0,) for e in entries)):
+                logits = self._graphed_forward(step)
+            else:
+                logits = self.model.forward(step, cache.views())
+        finally:
+            if carved:
+                ops.set_carveout(None)
         for e in entries:
             cache.commit(e.slot, cache.length[e.slot] + len(e.tokens))
         self.steps_run += 1

@@ -66,6 +66,8 @@ def library() -> ctypes.CDLL:
     lib.hfee_last_error.restype = ctypes.c_char_p
     lib.hfee_device_is_sm100.restype = _I
     lib.hfee_sm_count.restype = _I
+    lib.hfee_set_carveout.restype = _I
+    lib.hfee_set_carveout.argtypes = [_I]
     lib.hfee_gemm_skinny_splits.restype = _I
     lib.hfee_attention_tc_supports.restype = _I
     for name, sig in _SIGNATURES.items():
@@ -80,6 +82,14 @@ def library() -> ctypes.CDLL:
         raise KernelLibraryError(f"the kernels are built for sm_100a only; this device is sm_{major}{minor}")
     _LIB = lib
     return lib
+
+
+def set_carveout(percent: Optional[int]) -> Optional[int]:
+    """The split between shared memory and L1 that the launches that follow ask for: percent of the
+    SM's shared-memory maximum, or None for the driver's choice per kernel.  Returns the setting before.
+    A chain of short kernels runs fastest when all of them ask for the same split."""
+    before = library().hfee_set_carveout(-1 if percent is None else int(percent))
+    return None if before < 0 else before
 
 
 def sm_count() -> int:
