@@ -100,19 +100,16 @@ class ModelRunner:
         cache.sync()
         step = Step(entries, cache.length, self.buffers)
         step.feedback = self.feedback
-        carved = self.device.type == "cuda" and step.decode_only
-        if carved:
+        if self.device.type == "cuda":
+            # in effect until the next step: what runs between steps (sampling) belongs to the chain too
             from ..kernels import ops
-            ops.set_carveout(DECODE_CARVEOUT_MANY if step.r >= DECODE_MANY_REQUESTS else DECODE_CARVEOUT_FEW)
-        try:
-            if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
-                    and all(tuple(e.want) == (0,) for e in entries)):
-                logits = self._graphed_forward(step)
-            else:
-                logits = self.model.forward(step, cache.views())
-        finally:
-            if carved:
-                ops.set_carveout(None)
+            ops.set_carveout(None if not step.decode_only else
+                             DECODE_CARVEOUT_MANY if step.r >= DECODE_MANY_REQUESTS else DECODE_CARVEOUT_FEW)
+        if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
+                and all(tuple(e.want) == (0,) for e in entries)):
+            logits = self._graphed_forward(step)
+        else:
+            logits = self.model.forward(step, cache.views())
         for e in entries:
             cache.commit(e.slot, cache.length[e.slot] + len(e.tokens))
         self.steps_run += 1
