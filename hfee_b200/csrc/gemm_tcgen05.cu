@@ -40,7 +40,23 @@ constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ranges of K blocks
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
+
+// EPI_ROPE: the product is the fused q/k/v projection of a prompt portion, columns [q heads | k heads |
+// v heads] of head_dim each.  Instead of storing it, the epilogue rotates the query and key heads by
+// the token's position (hostfog/hfee internal/llm/forward.go:181-196, pairs (i, i + head_dim/2), or
+// (2i, 2i + 1) when `interleaved`) in float32, straight from the accumulator, writes the queries to
+// q_out and keys and values to the cache pages of (slot, position): the rotary kernel's pass over
+// the projection and the bfloat16 rounding between product and rotation fall away.
+struct RopeEpi {
+  const float2* cs;              // [token][head_dim/2] (cos, sin); null: no rotation
+  const int* positions;          // [token]
+  const int* slot_of_token;      // [token]
+  __nv_bfloat16* q_out; long long ld_q;
+  __nv_bfloat16* k_pool; __nv_bfloat16* v_pool;      // null: every head is a query head
+  PagedCache cache;
+  int heads, kv_heads, head_dim, interleaved;
+};
 
 template <int BN> struct TileCfg {
   static constexpr int STAGES = BN == 128 ? 6 : 4;
@@ -56,7 +72,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int reduce_by_tma,
                TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status,
-               float* __restrict__ sk_parts, int* __restrict__ sk_flags) {
+               float* __restrict__ sk_parts, int* __restrict__ sk_flags, const RopeEpi rope) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TMEM_COLS = ACC_STAGES * BN <= 256 ? 256 : 512;      // a power of two
@@ -218,6 +234,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // partial tiles are stored column by column (element (row, col) at col * 128 + row): a warp's
       // 32 rows of one column are 128 contiguous bytes
       float* my_part = contribute ? sk_parts + (long long)blockIdx.x * (BM * BN) + (quad * 32 + lane) : nullptr;
+      if constexpr (EPI == EPI_ROPE) {
+        // A unit is 64 columns of a head: the chunk of 32 dims d0 .. d0 + 31 and the chunk that holds
+        // their rotation partners (d + head_dim/2; with interleaved pairs simply the next chunk).  The two
+        // warps of a lane quadrant take every other unit.  BN is a multiple of head_dim: whole heads.
+        const int cph = rope.head_dim / 32;                    // chunks per head: 2 or 4
+        const bool row_ok = row < M;
+        int pos = 0, slot = 0;
+        if (row_ok) { pos = rope.positions[row]; slot = rope.slot_of_token[row]; }
+#pragma unroll 1
+        for (int u = half; u < BN / 64; u += 2) {
+          const int hh = (2 * u) / cph, pr = u % (cph / 2);
+          const int step_b = rope.interleaved ? 1 : cph / 2;
+          const int ch_a = rope.interleaved ? 2 * u : hh * cph + pr, ch_b = ch_a + step_b;
+          const int h = n0 / rope.head_dim + hh;               // the head's number among q, k and v heads
+          if (n0 + hh * rope.head_dim >= N) break;             // the same for the whole warp
+          uint32_t va[32], vb[32];
+          tc_ld32(tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch_a * 32), va);
+          tc_ld32(tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch_b * 32), vb);
+          tc_wait_ld();
+          if (!row_ok) continue;
+          __nv_bfloat16* dst;
+          bool rotate = rope.cs != nullptr;
+          if (h < rope.heads || rope.k_pool == nullptr) {
+            dst = rope.q_out + (long long)row * rope.ld_q + (long long)h * rope.head_dim;
+          } else if (h < rope.heads + rope.kv_heads) {
+            dst = rope.k_pool + paged_offset(rope.cache, slot, pos, h - rope.heads);
+          } else {
+            dst = rope.v_pool + paged_offset(rope.cache, slot, pos, h - rope.heads - rope.kv_heads);
+            rotate = false;
+          }
+          const int da = (ch_a - hh * cph) * 32, db = (ch_b - hh * cph) * 32;      // first dims of the two chunks
+          if (rotate) {
+            const float2* t = rope.cs + (long long)row * (rope.head_dim / 2);
+            if (!rope.interleaved) {
+              // va holds dims da + j, vb their partners da + j + head_dim/2; table entry da + j
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float4 c = __ldg(reinterpret_cast<const float4*>(t + da + j));
+                const float x0 = __uint_as_float(va[j]), y0 = __uint_as_float(vb[j]);
+                const float x1 = __uint_as_float(va[j + 1]), y1 = __uint_as_float(vb[j + 1]);
+                va[j] = __float_as_uint(x0 * c.x - y0 * c.y);     vb[j] = __float_as_uint(x0 * c.y + y0 * c.x);
+                va[j + 1] = __float_as_uint(x1 * c.z - y1 * c.w); vb[j + 1] = __float_as_uint(x1 * c.w + y1 * c.z);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 ca = __ldg(reinterpret_cast<const float4*>(t + (da + j) / 2));
+                const float4 cb = __ldg(reinterpret_cast<const float4*>(t + (db + j) / 2));
+                float x0 = __uint_as_float(va[j]), x1 = __uint_as_float(va[j + 1]);
+                va[j] = __float_as_uint(x0 * ca.x - x1 * ca.y); va[j + 1] = __float_as_uint(x0 * ca.y + x1 * ca.x);
+                x0 = __uint_as_float(va[j + 2]); x1 = __uint_as_float(va[j + 3]);
+                va[j + 2] = __float_as_uint(x0 * ca.z - x1 * ca.w); va[j + 3] = __float_as_uint(x0 * ca.w + x1 * ca.z);
+                x0 = __uint_as_float(vb[j]); x1 = __uint_as_float(vb[j + 1]);
+                vb[j] = __float_as_uint(x0 * cb.x - x1 * cb.y); vb[j + 1] = __float_as_uint(x0 * cb.y + x1 * cb.x);
+                x0 = __uint_as_float(vb[j + 2]); x1 = __uint_as_float(vb[j + 3]);
+                vb[j + 2] = __float_as_uint(x0 * cb.z - x1 * cb.w); vb[j + 3] = __float_as_uint(x0 * cb.w + x1 * cb.z);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 oa, ob;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(va[j]), __uint_as_float(va[j + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(va[j + 2]), __uint_as_float(va[j + 3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(va[j + 4]), __uint_as_float(va[j + 5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(va[j + 6]), __uint_as_float(va[j + 7]));
+            oa.x = *reinterpret_cast<uint32_t*>(&p0); oa.y = *reinterpret_cast<uint32_t*>(&p1);
+            oa.z = *reinterpret_cast<uint32_t*>(&p2); oa.w = *reinterpret_cast<uint32_t*>(&p3);
+            p0 = __floats2bfloat162_rn(__uint_as_float(vb[j]), __uint_as_float(vb[j + 1]));
+            p1 = __floats2bfloat162_rn(__uint_as_float(vb[j + 2]), __uint_as_float(vb[j + 3]));
+            p2 = __floats2bfloat162_rn(__uint_as_float(vb[j + 4]), __uint_as_float(vb[j + 5]));
+            p3 = __floats2bfloat162_rn(__uint_as_float(vb[j + 6]), __uint_as_float(vb[j + 7]));
+            ob.x = *reinterpret_cast<uint32_t*>(&p0); ob.y = *reinterpret_cast<uint32_t*>(&p1);
+            ob.z = *reinterpret_cast<uint32_t*>(&p2); ob.w = *reinterpret_cast<uint32_t*>(&p3);
+            *reinterpret_cast<uint4*>(dst + da + j) = oa;
+            *reinterpret_cast<uint4*>(dst + db + j) = ob;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int cc = 0; cc < CHUNKS; ++cc) {
         const int ch = half * CHUNKS + cc;
@@ -338,6 +433,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
+      }
       // this warp's reads of the accumulator are complete: hand the buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -411,7 +507,7 @@ int make_map_c(CUtensorMap* map, void* base, long long rows, long long cols, lon
 
 template <int BN, int EPI, typename TOut>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
-           float* workspace, long long workspace_floats, int* flags, cudaStream_t stream) {
+           float* workspace, long long workspace_floats, int* flags, cudaStream_t stream, const RopeEpi& rope = RopeEpi{}) {
   using Cfg = TileCfg<BN>;
   // accumulate: by bulk tensor reduction when C can have a tensor map (16-byte aligned base and pitch)
   CUtensorMap mc = ma;
@@ -433,7 +529,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
   const int sk_ctas = (workspace && flags) ? plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, BN) : 0;
   dim3 grid((unsigned)(sk_ctas ? sk_ctas : (tiles < sms ? tiles : sms)));          // one CTA per SM
   hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status,
-              sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr);
+              sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr, rope);
   return hfee_check_launch("gemm_tcgen05");
 }
 
@@ -490,4 +586,58 @@ HFEE_API int hfee_gemm_tcgen05_stream_k(int M, int N, int K, int block_n, long l
   if (sms <= 0) return 0;
   long long tiles = (long long)((M + BM - 1) / BM) * ((N + block_n - 1) / block_n);
   return plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, block_n);
+}
+
+// 1 if hfee_gemm_tcgen05_rope takes these head sizes (bfloat16 implied): heads of 64 or 128 dims, all
+// of them rotated.
+HFEE_API int hfee_gemm_tcgen05_rope_supports(int head_dim, int rope_dim) {
+  return (head_dim == 64 || head_dim == 128) && rope_dim == head_dim ? 1 : 0;
+}
+
+// The q/k/v projection of prompt tokens with rotation and cache write in its epilogue (see RopeEpi):
+// A [M, K] tokens, W [N, K] with N = (heads + 2 kv_heads) * head_dim rows [q heads | k heads | v heads],
+// or N = heads * head_dim and null pools for a run that reads another run's cache.  cs [M, head_dim/2]
+// (cos, sin) pairs or null; queries go to q_out [M, ld_q], keys and values to the pages of
+// (slot_of_token, positions).
+HFEE_API int hfee_gemm_tcgen05_rope(const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
+                                    const float* cs, const int* positions, const int* slot_of_token, void* q_out,
+                                    long long ld_q, void* k_pool, void* v_pool, const int* block_table, int max_pages,
+                                    int page_size, int heads, int kv_heads, int head_dim, int interleaved, int* status,
+                                    cudaStream_t stream) {
+  if (M == 0 || N == 0) return HFEE_OK;
+  HFEE_REQUIRE(hfee_gemm_tcgen05_rope_supports(head_dim, head_dim), "gemm_tcgen05_rope: head_dim %d is not 64 or 128", head_dim);
+  HFEE_REQUIRE(M > 0 && K > 0 && K % 8 == 0, "gemm_tcgen05_rope: K=%d must be a positive multiple of 8", K);
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0,
+               "gemm_tcgen05_rope: operands must be 16-byte aligned with leading dimensions that are multiples of 8 and at least K");
+  HFEE_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "gemm_tcgen05_rope: key and value pools go together");
+  HFEE_REQUIRE(N == (heads + (k_pool ? 2 * kv_heads : 0)) * head_dim, "gemm_tcgen05_rope: N=%d is not the width of the heads", N);
+  HFEE_REQUIRE(ld_q % 8 == 0 && ld_q >= (long long)heads * head_dim && (uintptr_t)q_out % 16 == 0 &&
+               (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cs % 16 == 0,
+               "gemm_tcgen05_rope: outputs and the table must be 16-byte aligned");
+  RopeEpi rope;
+  rope.cs = (const float2*)cs; rope.positions = positions; rope.slot_of_token = slot_of_token;
+  rope.q_out = (__nv_bfloat16*)q_out; rope.ld_q = ld_q;
+  rope.k_pool = (__nv_bfloat16*)k_pool; rope.v_pool = (__nv_bfloat16*)v_pool;
+  HFEE_REQUIRE(make_paged_cache(&rope.cache, block_table, max_pages, page_size, kv_heads, head_dim),
+               "gemm_tcgen05_rope: page_size %d must be a power of two", page_size);
+  rope.heads = heads; rope.kv_heads = kv_heads; rope.head_dim = head_dim; rope.interleaved = interleaved;
+  // tiles of whole heads: 256 columns, or 128 where those fill the SMs better
+  const int sms = hfee_sm_count();
+  const long long tiles_256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  int bn = tiles_256 >= 96 || sms <= 0 ? 256 : 128;
+  if (bn == 256 && head_dim == 64 && sms > 0) {
+    // three heads wide where that saves a round of tiles (16 x 12 tiles of 256 are two rounds on 148 SMs
+    // with the second a third full; 16 x 16 tiles of 192 are two rounds of three quarters the work)
+    const long long m_tiles = (M + BM - 1) / BM;
+    const long long rounds_192 = (m_tiles * ((N + 191) / 192) + sms - 1) / sms, rounds_256 = (tiles_256 + sms - 1) / sms;
+    if (rounds_192 * 192 * 105 < rounds_256 * 256 * 100) bn = 192;
+  }
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc != HFEE_OK) return rc;
+  rc = make_map(&mw, W, N, K, ldw, bn);
+  if (rc != HFEE_OK) return rc;
+  if (bn == 256) return launch<256, EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, nullptr, 0, nullptr, stream, rope);
+  if (bn == 192) return launch<192, EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, nullptr, 0, nullptr, stream, rope);
+  return launch<128, EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, nullptr, 0, nullptr, stream, rope);
 }

@@ -25,8 +25,8 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 # batch 2 / 4 / 8 / 16 / 32: 0.752 / 0.806 / 0.833 / 1.043 / 1.394 against 0.761 / 0.818 / 0.861 /
 # 1.064 / 1.404 (more shared memory than that starves the kernels that stream weights through L1: 100 %
 # at batch 8 takes 1.135); at batch 64, where attention is half the step and wants three CTAs of 76 KB
-# per SM, 100 % takes 1.78 against 1.85.
-DECODE_CARVEOUT_FEW, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 48
+# per SM, 100 % takes 1.78 against 1.85.  A prompt of 2,048 tokens: 4.29 ms at 58 % against 4.35.
+STEP_CARVEOUT, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 48
 DEVICE_TOKEN = -1        # as a single-token entry: "the token the device sampled last for this request"
 
 
@@ -103,8 +103,8 @@ class ModelRunner:
         if self.device.type == "cuda":
             # in effect until the next step: what runs between steps (sampling) belongs to the chain too
             from ..kernels import ops
-            ops.set_carveout(None if not step.decode_only else
-                             DECODE_CARVEOUT_MANY if step.r >= DECODE_MANY_REQUESTS else DECODE_CARVEOUT_FEW)
+            ops.set_carveout(DECODE_CARVEOUT_MANY if step.decode_only and step.r >= DECODE_MANY_REQUESTS
+                             else STEP_CARVEOUT)
         if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
                 and all(tuple(e.want) == (0,) for e in entries)):
             logits = self._graphed_forward(step)

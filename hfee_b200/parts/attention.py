@@ -61,19 +61,22 @@ class PagedAttention(Mixer):
         n, rt = step.n, self.rt
         cs = self.position.table(step)
         q = rt.scratch("attn_q", (rt.max_tokens, self.q_cols))[:n]
-        if writes_cache:
-            qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n]
-            ops.tag("qkv")
-            ops.linear_normed(xn, self.w_qkv, qkv)
-            k_pool, v_pool = cache.k, cache.v
-        else:       # reads the cache another run filled: only the queries are needed
-            qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n, :self.q_cols]
-            ops.tag("qkv")
-            ops.linear_normed(xn, self.w_qkv[:self.q_cols], qkv)
-            k_pool = v_pool = None
+        # a run that reads the cache another run filled needs the queries only
+        w = self.w_qkv if writes_cache else self.w_qkv[:self.q_cols]
+        qkv = rt.scratch("attn_qkv", (rt.max_tokens, self.qkv_cols))[:n, :w.shape[0]]
+        k_pool, v_pool = (cache.k, cache.v) if writes_cache else (None, None)
+        decode = ops.decode_rope_fusable(step, qkv.dtype, self.heads, self.kv_heads, self.head_dim,
+                                         self.position.rope_dim, qkv, self.split_scratch)
+        fused_qkv = not decode and ops.qkv_rope_fusable(rt.dtype, n, w, self.head_dim, self.position.rope_dim, cs, q)
+        ops.tag("qkv")
+        if fused_qkv:            # a prompt portion: rotation and cache write happen in the product's epilogue
+            ops.linear_rope_cache(xn if isinstance(xn, torch.Tensor) else xn.tensor(), w, cs, step.positions,
+                                  step.slot_of_token, q, k_pool, v_pool, cache.block_table, cache.page_size,
+                                  self.heads, self.kv_heads, self.head_dim, self.position.interleaved)
+        else:
+            ops.linear_normed(xn, w, qkv)
         att = rt.scratch("attn_out", (rt.max_tokens, self.q_cols))[:n]
-        if ops.decode_rope_fusable(step, qkv.dtype, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
-                                   qkv, self.split_scratch):
+        if decode:
             # a decode step: rotation and cache write happen inside the attention kernel
             ops.tag("attention")
             ops.paged_attention_rope(qkv, cs, self.position.rope_dim, self.position.interleaved, writes_cache,
@@ -83,8 +86,9 @@ class PagedAttention(Mixer):
             ops.tag("o")
             ops.linear(att, self.w_o, residual, accumulate=True)
             return
-        ops.tag("rope")
-        ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
+        if not fused_qkv:
+            ops.tag("rope")
+            ops.rope_cache_write(qkv, cs, step.positions, step.slot_of_token, q, k_pool, v_pool, cache.block_table,
                              cache.page_size, self.heads, self.kv_heads, self.head_dim, self.position.rope_dim,
                              self.position.interleaved)
         ops.tag("attention")

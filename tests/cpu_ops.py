@@ -141,3 +141,4 @@ def install(monkeypatch):
     monkeypatch.setattr(ops, "ARGMAX_CHUNKS", 1, raising=False)
     # kernel fusions have no double: the parts take their unfused paths
     monkeypatch.setattr(ops, "FUSE_ROPE_INTO_DECODE_ATTENTION", False, raising=False)
+    monkeypatch.setattr(ops, "FUSE_ROPE_INTO_QKV", False, raising=False)

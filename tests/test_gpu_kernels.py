@@ -112,6 +112,58 @@ def test_rope_cache_write(ops, dtype, heads, kv, hd, rope_dim, inter):
     assert int((kp.float().abs().sum(-1) > 0).sum()) == written * kv       # nothing else was touched
 
 
+@pytest.mark.parametrize("heads,kv,hd,inter,n,k,page", [(4, 2, 64, False, 200, 256, 16), (3, 1, 128, False, 130, 192, 64),
+                                                       (5, 5, 64, True, 129, 64, 16), (2, 1, 128, True, 300, 320, 32),
+                                                       (32, 8, 64, False, 2048, 2048, 64), (6, 2, 64, False, 1100, 520, 64)])
+@pytest.mark.parametrize("with_cache", [True, False])
+def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(ops, heads, kv, hd, inter, n, k, page, with_cache):
+    """Token rows that do not fill the last tile of 128, head counts that do not fill the last tile of
+    256 columns, several requests whose tokens lie on pages in shuffled order; with the pools, and for a
+    run that only needs the queries."""
+    g = torch.Generator().manual_seed(23)
+    slots = 3
+    per = -(-n // slots)
+    max_pages = -(-(per + 7) // page) + 1
+    cols = (heads + 2 * kv) * hd if with_cache else heads * hd
+    a = (torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(cols, k, generator=g) * (1.0 / k ** 0.5)).to(torch.bfloat16).to(DEV)
+    slot = (torch.arange(n) % slots).to(torch.int32)
+    pos = (torch.arange(n) // slots + 7).to(torch.int32)          # distinct (slot, position) pairs, page edges inside
+    table = torch.randperm(slots * max_pages, generator=g).reshape(slots, max_pages).to(torch.int32).to(DEV)
+    kp = torch.full((slots * max_pages, kv, page, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vp = torch.full_like(kp, float("nan"))
+    q = torch.full((n, heads * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * i / hd)) for i in range(hd // 2)], dtype=torch.float64, device=DEV)
+    cs = torch.empty(n, hd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(pos.to(DEV), inv, cs)
+    assert ops.qkv_rope_fusable(torch.bfloat16, n, w, hd, hd, cs, q)
+    ops.linear_rope_cache(a, w, cs, pos.to(DEV), slot.to(DEV), q, kp if with_cache else None, vp if with_cache else None,
+                          table, page, heads, kv, hd, inter)
+    ops.check_status()
+
+    x = (a.double() @ w.double().t()).cpu().reshape(n, -1, hd)
+    rotated = heads + kv if with_cache else heads
+    ang = pos.double()[:, None] * inv.cpu()[None, :]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    rot = x[:, :rotated].clone()
+    if inter:
+        u, v = x[:, :rotated, 0::2], x[:, :rotated, 1::2]
+        rot[..., 0::2], rot[..., 1::2] = u * c - v * s, u * s + v * c
+    else:
+        u, v = x[:, :rotated, :hd // 2], x[:, :rotated, hd // 2:]
+        rot[..., :hd // 2], rot[..., hd // 2:] = u * c - v * s, u * s + v * c
+    _close(q, rot[:, :heads].reshape(n, -1), 6e-3)
+    if not with_cache:
+        assert bool(torch.isnan(kp.float()).all())
+        return
+    pages = table.cpu()[slot.long(), (pos // page).long()].long()
+    in_page = (pos % page).long()
+    _close(kp[pages.to(DEV), :, in_page.to(DEV)], rot[:, heads:], 6e-3)
+    _close(vp[pages.to(DEV), :, in_page.to(DEV)], x[:, heads + kv:], 6e-3)
+    # nothing else was touched
+    assert int((~torch.isnan(kp.float()).any(-1)).sum()) == n * kv and int((~torch.isnan(vp.float()).any(-1)).sum()) == n * kv
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,inter,granule", [(3, 172, None), (7, 172, 4), (2, 8192, 4), (1, 5, None)])
 def test_swiglu(ops, dtype, n, inter, granule):
