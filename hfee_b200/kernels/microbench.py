@@ -2,6 +2,7 @@
 where that matters, and prints what it achieved against the roofline that bounds it.
 
     python -m hfee_b200.kernels.microbench gemm_tcgen05 --m 2048 --n 16384 --k 2048 [--epilogue swiglu]
+    python -m hfee_b200.kernels.microbench gemm_pair    --m 2048 --n 16384 --k 2048 --epilogue swiglu
     python -m hfee_b200.kernels.microbench gemm_stream  --m 8 --n 16384 --k 2048 [--epilogue swiglu]
     python -m hfee_b200.kernels.microbench gemm_ring    --m 8 --n 2048 --k 8192 --epilogue accum
     python -m hfee_b200.kernels.microbench gemm_skinny  --m 64 --n 2048 --k 8192 --epilogue accum
@@ -71,6 +72,8 @@ def _gemm(args, kind: str) -> dict:
         fn = lambda i: ops.gemm_tcgen05(a, ws[i % len(ws)], out, epi, args.block_n)
     elif kind == "gemm_skinny":
         fn = lambda i: ops.gemm_skinny(a, ws[i % len(ws)], out, epi)
+    elif kind == "gemm_pair":
+        fn = lambda i: ops.gemm_tcgen05_pair(a, ws[i % len(ws)], out, epi)
     elif kind == "gemm_ring":
         fn = lambda i: ops.gemm_ring(a, ws[i % len(ws)], out, epi)
     else:
@@ -127,7 +130,7 @@ def _attention(args, decode: bool) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "attention_decode", "attention_prefill"])
+    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)

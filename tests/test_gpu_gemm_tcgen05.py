@@ -60,6 +60,73 @@ def test_swiglu_epilogue(m, inner, k, block_n):
     assert _err(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
 
 
+PAIR_SHAPES = [(256, 256, 64), (128, 256, 128), (65, 8, 8), (200, 300, 96), (257, 513, 72), (1000, 96, 2048),
+               (2048, 2048, 2048), (333, 1000, 8192), (2048 + 128, 4096, 520)]
+
+
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_pairs_of_ctas_store_and_accumulate(m, n, k):
+    """Two CTAs on a tile of 256 x 256: whole tiles, a pair whose second CTA has no rows (128, 65), rows
+    and columns that end inside a tile, a K that is no multiple of 64, more tiles than pairs of SMs."""
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(m * 5 + n * 3 + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    ref = a.double().cpu() @ w.double().cpu().t()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05_pair(a, w, out, ops.EPI_STORE)
+    ops.check_status()
+    assert _err(out, ref) < _f32_tol(k)
+    outb = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05_pair(a, w, outb, ops.EPI_STORE)
+    assert _err(outb, ref) < 6e-3
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops.gemm_tcgen05_pair(a, w, acc, ops.EPI_ACCUM)
+    ops.check_status()
+    assert _err(acc, base.double().cpu() + ref) < _f32_tol(k)
+    # a start and a pitch the bulk reduction cannot take: the plain read-add-write epilogue
+    view = torch.zeros(m, n + 3, dtype=torch.float32, device=DEV)[:, 1:n + 1]
+    view.copy_(base)
+    ops.gemm_tcgen05_pair(a, w, view, ops.EPI_ACCUM)
+    ops.check_status()
+    assert _err(view, base.double().cpu() + ref) < _f32_tol(k)
+
+
+@pytest.mark.parametrize("m,inner,k", [(256, 128, 64), (300, 172, 96), (2048, 8192, 2048), (70, 1000, 264), (520, 1000, 4096)])
+def test_pairs_of_ctas_swiglu(m, inner, k):
+    from hfee_b200.kernels import ops
+    g = torch.Generator().manual_seed(inner + 1)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) * 0.1).to(torch.bfloat16)
+    w = torch.stack([gate.reshape(inner // 4, 4, k), up.reshape(inner // 4, 4, k)], 1).reshape(2 * inner, k).contiguous().to(DEV)
+    out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05_pair(a, w, out, ops.EPI_SWIGLU)
+    ops.check_status()
+    gd, ud = a.double().cpu() @ gate.double().t(), a.double().cpu() @ up.double().t()
+    assert _err(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
+
+
+def test_the_dispatcher_takes_pairs_for_the_large_products_of_a_prompt(monkeypatch):
+    """A large accumulating product of a 2,048-token prompt goes to the pair kernel and gives what the
+    single-CTA kernel gives."""
+    from hfee_b200.kernels import ops
+    calls = []
+    real = ops.gemm_tcgen05_pair
+    monkeypatch.setattr(ops, "gemm_tcgen05_pair", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(2048, 1024, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(4096, 1024, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    base = torch.randn(2048, 4096, generator=g).to(DEV)
+    got, ref = base.clone(), base.clone()
+    ops.gemm_tcgen05(a, w, got, ops.EPI_ACCUM)
+    assert calls == [1]
+    ops.gemm_tcgen05(a, w, ref, ops.EPI_ACCUM, block_n=256)
+    ops.check_status()
+    assert _err(got, ref.double().cpu()) < 1e-6
+
+
 @pytest.mark.parametrize("m,n,k", [(512, 2048, 8192), (256, 2048, 8192), (333, 1000, 8192), (130, 300, 4104), (1000, 500, 6000)])
 def test_split_by_k_blocks_matches_whole_tiles(m, n, k):
     """Shapes with tiles for less than half of the SMs and a long K are split by K blocks among the
