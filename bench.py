@@ -157,6 +157,7 @@ def reference_arm():
 
 
 def main():
+    global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -172,6 +173,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="profiling aid: run just one of the measurements (the JSON line is then partial)")
+    ap.add_argument("--prompt", type=int, default=PROMPT,
+                    help="tokens of the prompts (other context lengths than the headline's 2,048; the cache holds twice as many per request)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -180,6 +183,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.prompt != PROMPT:
+        PROMPT, CONTEXT = args.prompt, max(CONTEXT, 2 * args.prompt)
 
     import numpy as np
     import torch
@@ -193,6 +198,7 @@ def main():
     f32 = args.dtype == "float32"
     elem = 4 if f32 else 2
     cfg = dict(model, num_hidden_layers=layers)
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], CONTEXT)
     nums = model_numbers(cfg, layers, elem)
     context = min(CONTEXT, cfg["max_position_embeddings"])
     if f32:      # no tensor cores on this path: FFMA rate of this device at its highest clock

@@ -27,6 +27,10 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 # at batch 8 takes 1.135); at batch 64, where attention is half the step and wants three CTAs of 76 KB
 # per SM, 100 % takes 1.78 against 1.85.  A prompt of 2,048 tokens: 4.29 ms at 58 % against 4.35.
 STEP_CARVEOUT, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 48
+# Steps of up to this many tokens are replayed from CUDA graphs once their shape has been seen twice: the
+# host needs about 2 ms to launch a pass of a 16-layer model whatever its size, the GPU less than that
+# below about 1,000 tokens.  At most GRAPH_LIMIT graphs are kept.
+GRAPH_MAX_TOKENS, GRAPH_LIMIT = 1024, 64
 DEVICE_TOKEN = -1        # as a single-token entry: "the token the device sampled last for this request"
 
 
@@ -105,9 +109,9 @@ class ModelRunner:
             from ..kernels import ops
             ops.set_carveout(DECODE_CARVEOUT_MANY if step.decode_only and step.r >= DECODE_MANY_REQUESTS
                              else STEP_CARVEOUT)
-        if (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda" and step.decode_only
-                and all(tuple(e.want) == (0,) for e in entries)):
-            logits = self._graphed_forward(step)
+        key = self._graph_key(step, entries)
+        if key is not None:
+            logits = self._graphed_forward(step, key)
         else:
             logits = self.model.forward(step, cache.views())
         for e in entries:
@@ -116,13 +120,28 @@ class ModelRunner:
         self.last_step = step
         return logits
 
-    def _graphed_forward(self, step: Step) -> torch.Tensor:
-        """A decode-only step through a CUDA graph keyed by its batch size.  The step's integers
-        live at the same device addresses for every step of that size and are copied in before the
+    def _graph_key(self, step: Step, entries: Sequence[StepEntry]):
+        """What a captured step can be replayed for, or None for a step that runs eagerly.  Everything
+        the kernels of a graph-safe model read of a step lies in device buffers whose addresses depend
+        only on the numbers of tokens, requests and wanted rows; what the launches themselves depend on
+        (grids, the choice of kernels) follows from the token count of each request.  Decode-only steps
+        that want every request's logits are keyed by their batch size; other steps of at most
+        GRAPH_MAX_TOKENS tokens (prompt portions under a token budget, alone or beside decoded tokens,
+        which the host cannot launch as fast as the GPU runs them) by the counts in batch order."""
+        if not (self.engine.use_cuda_graphs and self.model.graph_safe and self.device.type == "cuda"):
+            return None
+        if step.decode_only and all(tuple(e.want) == (0,) for e in entries):
+            return step.r
+        if step.n <= GRAPH_MAX_TOKENS:
+            return (tuple(len(e.tokens) for e in entries), step.n_logits)
+        return None
+
+    def _graphed_forward(self, step: Step, key) -> torch.Tensor:
+        """A step through a CUDA graph.  The step's integers
+        live at the same device addresses for every step of that key and are copied in before the
         replay, block tables likewise; launch parameters that depend on context lengths are planned
         for the longest context the engine allows."""
         from ..kernels import ops
-        key = step.r
         step.planning_context = self.cache.max_context
         hit = self._graphs.get(key)
         if hit is None:
@@ -134,6 +153,8 @@ class ModelRunner:
             torch.cuda.synchronize()
             with torch.cuda.graph(graph):
                 out = self.model.forward(step, self.cache.views())
+            while len(self._graphs) >= GRAPH_LIMIT:          # oldest first
+                self._graphs.pop(next(iter(self._graphs)))
             hit = self._graphs[key] = (graph, out, ops.launch_count() - before)
         graph, out, kernels = hit
         graph.replay()

@@ -97,10 +97,16 @@ def set_carveout(percent: Optional[int]) -> Optional[int]:
 
 def sm_count() -> int:
     """Streaming multiprocessors of the current device, as the kernels' launchers see them."""
-    n = library().hfee_sm_count()
-    if n <= 0:
-        raise KernelLibraryError("cannot ask the device for its number of SMs")
-    return n
+    global _SMS
+    if _SMS is None:
+        n = library().hfee_sm_count()
+        if n <= 0:
+            raise KernelLibraryError("cannot ask the device for its number of SMs")
+        _SMS = n
+    return _SMS
+
+
+_SMS: Optional[int] = None
 
 
 def loaded_library_path() -> Optional[str]:
@@ -161,8 +167,28 @@ def _check(code: int, lib: ctypes.CDLL) -> None:
         raise KernelLibraryError(lib.hfee_last_error().decode() or f"kernel call failed with code {code}")
 
 
+_STREAM_HELD: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _STREAM_HELD if _STREAM_HELD is not None else torch.cuda.current_stream().cuda_stream
+
+
+class stream_held:
+    """``with ops.stream_held():`` every launch inside goes to the stream that is current at entry,
+    asked of torch once instead of once per launch (a third of the host's time for a prompt pass of a
+    16-layer model went into that question).  Nothing inside may change the current stream."""
+
+    def __enter__(self):
+        global _STREAM_HELD
+        self.before = _STREAM_HELD
+        _STREAM_HELD = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _STREAM_HELD
+        _STREAM_HELD = self.before
+        return False
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -347,8 +373,14 @@ def gemm_ring(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
                               _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _status().data_ptr(), _stream()), lib)
 
 
+_RING_TAKES: dict = {}
+
+
 def ring_takes(m: int, n: int, k: int, epilogue: int) -> bool:
-    return bool(library().hfee_gemm_ring_supports(m, n, k, epilogue))
+    key = (m, n, k, epilogue)
+    if key not in _RING_TAKES:
+        _RING_TAKES[key] = bool(library().hfee_gemm_ring_supports(*key))
+    return _RING_TAKES[key]
 
 
 def _status() -> torch.Tensor:
@@ -658,8 +690,14 @@ def attention_tc(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, co
                                  float(scale), int(window or 0), _status().data_ptr(), _stream()), lib)
 
 
+_TC_TAKES: dict = {}
+
+
 def attention_tc_supports(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    return bool(library().hfee_attention_tc_supports(heads, kv_heads, head_dim, page_size))
+    key = (heads, kv_heads, head_dim, page_size)
+    if key not in _TC_TAKES:
+        _TC_TAKES[key] = bool(library().hfee_attention_tc_supports(*key))
+    return _TC_TAKES[key]
 
 
 def paged_attention(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,

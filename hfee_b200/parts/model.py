@@ -98,6 +98,13 @@ class DecoderModel:
     def forward(self, step: Any, caches: Mapping[int, Any]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every scheduled layer; returns float32 logits
         [len(step.logit_rows), vocab] (None if no logits are wanted)."""
+        if self.rt.device.type != "cuda":
+            return self._forward(step, caches)
+        from ..kernels import ops
+        with ops.stream_held():          # one stream for the whole pass, looked up once
+            return self._forward(step, caches)
+
+    def _forward(self, step: Any, caches: Mapping[int, Any]) -> Optional[torch.Tensor]:
         rt = self.rt
         residual = rt.scratch("residual", (rt.max_tokens, self.width), torch.float32)[:step.n]
         self.embedding.forward(step, residual)

@@ -65,6 +65,27 @@ def test_replay(tiny_dirs, refs, name, dtype, scheme):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("scheme", ["equal_portions", "two_sizes", "mixed"])
+def test_steps_whose_shape_repeats_replay_from_cuda_graphs(tiny_dirs, refs, name, dtype, scheme):
+    """Prompt portions of one size (the usual case under a token budget), of two alternating sizes, and
+    mixed steps: from the third step of a shape on they are replayed from a captured graph, at other
+    positions, on other pages and for other requests than the captured step's."""
+    from hfee_b200 import EngineConfig, ModelRunner
+    cfg, seqs, ref = refs[name, dtype]
+    if scheme == "mixed":
+        steps, tokens = ru.mixed(seqs, live=4, seed=2, chunk_sizes=(2, 5, 16)), 17 * 16
+    else:
+        steps, tokens = ru.portions(seqs, sizes=(8,) if scheme == "equal_portions" else (16, 3)), 112
+    e = EngineConfig(dtype=dtype, page_size=16, max_requests=4, max_context=tokens, max_cache_tokens=tokens,
+                     max_batch_tokens=tokens, use_cuda_graphs=True)
+    runner = ModelRunner(tiny_dirs[name], e)
+    got = ru.run_in_process(runner, steps)
+    check(got, seqs, ref, dtype)
+    assert runner.graph_replays >= (20 if scheme != "mixed" else 1), runner.graph_replays
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_binary(tiny_dirs, refs, tmp_path, dtype):
     cfg, seqs, ref = refs["B", dtype]
     steps = ru.mixed(seqs, live=4, seed=4)
