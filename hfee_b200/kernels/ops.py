@@ -642,9 +642,18 @@ def attention_splits(requests: int, kv_heads: int, max_context: int, sms: Option
     11.3 / 30.9 / 99.6 us at 2,048 / 8,192 / 32,768 keys; batch 12 at 8,192 keys: 6 against 4 take
     37.5 against 42.6 us), and at least four even when the batch alone would fill the GPU (shorter
     CTAs balance better and keep more loads in flight: at 2,048 keys, batch 32: 41.8 us unsplit,
-    33.4 us with four), but at least two key blocks of 64 each."""
-    want = max(4, 4 * (sms or sm_count()) // max(1, requests * kv_heads))
+    33.4 us with four), but at least two key blocks of 64 each.  With few (request, kv head) pairs,
+    two CTAs per SM: those grids take the kernel variant with four key blocks in flight per CTA, of
+    which the step's shared-memory carve-out holds one per SM (decode step of the benchmark model at
+    batch 2 / 3 / 4 / 5 / 6: 0.742 / 0.777 / 0.786 / 0.802 / 0.817 ms against 0.755 / 0.798 / 0.809 /
+    0.812 / 0.823 with four per SM; at batch 8: 0.857 against 0.838)."""
+    pairs = max(1, requests * kv_heads)
+    per_sm = 2 if pairs <= FEW_PAIRS else 4
+    want = max(4, per_sm * (sms or sm_count()) // pairs)
     return max(1, min(MAX_SPLITS, want, max_context // 128))
+
+
+FEW_PAIRS = 48
 
 
 def attention_mma(q, k_pool, v_pool, block_table, page_size, cu_tokens, slots, context_before, out, n_tokens,

@@ -26,6 +26,11 @@ def test_key_splits_fill_the_gpu_about_once(sms):
     assert 3 * sms < s * 64 <= 4 * sms
     # a batch that fills the GPU by itself is still split in four
     assert ops.attention_splits(64, 8, 2048, sms) == 4
-    # more requests never get more splits each
-    per_batch = [ops.attention_splits(r, 8, 1 << 16, sms) for r in range(1, 80)]
-    assert all(a >= b for a, b in zip(per_batch, per_batch[1:]))
+    # few (request, kv head) pairs: about two CTAs per SM (those grids run the kernel variant of which an SM holds one)
+    for r in (3, 4, 6):
+        s = ops.attention_splits(r, 8, 32768, sms)
+        assert sms < s * r * 8 <= 2 * sms
+    # within either rule more requests never get more splits each
+    few = [ops.attention_splits(r, 8, 1 << 16, sms) for r in range(1, ops.FEW_PAIRS // 8 + 1)]
+    many = [ops.attention_splits(r, 8, 1 << 16, sms) for r in range(ops.FEW_PAIRS // 8 + 1, 80)]
+    assert all(a >= b for a, b in zip(few, few[1:])) and all(a >= b for a, b in zip(many, many[1:]))
