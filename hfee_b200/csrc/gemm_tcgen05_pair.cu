@@ -19,6 +19,7 @@
 // Every wait has a time limit; a wait that runs out sets the status word, and the CTAs of a pair
 // meet once more before they free tensor memory and leave.
 #include "tcgen05.cuh"
+#include "rope_epilogue.cuh"
 
 namespace {
 
@@ -37,7 +38,7 @@ constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
 constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -82,7 +83,7 @@ template <int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_c, int reduce_by_tma,
-                 TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status) {
+                 TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status, const RopeEpi rope) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];         // used in the even CTA: both CTAs' loads of a stage
   __shared__ __align__(8) uint64_t empty_bar[STAGES];        // in each CTA: the MMAs that read the stage are done
@@ -186,6 +187,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       if (!ok) break;
       const int row = m0 + quad * 32 + lane;
+      if constexpr (EPI == EPI_ROPE) {
+        rope_epilogue<BN>(rope, tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16), half, row, M, N, n0);
+      } else {
 #pragma unroll 1
       for (int cc = 0; cc < CHUNKS; ++cc) {
         const int ch = half * CHUNKS + cc;
@@ -280,6 +284,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+      }
       // this warp's reads of the accumulator are complete: tell the even CTA's MMA warp
       tc_fence_before();
       __syncwarp();
@@ -322,7 +327,7 @@ int make_map_c(CUtensorMap* map, void* base, long long rows, long long cols, lon
 
 template <int EPI, typename TOut>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, const RopeEpi& rope = RopeEpi{}) {
   CUtensorMap mc = ma;
   int reduce_by_tma = 0;
   if (EPI == EPI_ACCUM && (uintptr_t)C % 16 == 0 && ldc % 4 == 0) {
@@ -358,7 +363,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long
     attr[2].val.sharedMemCarveout = (unsigned int)carve;
     cfg.numAttrs = 3;
   }
-  cudaLaunchKernelEx(&cfg, gemm_pair_kernel<EPI, TOut>, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status);
+  cudaLaunchKernelEx(&cfg, gemm_pair_kernel<EPI, TOut>, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status, rope);
   return hfee_check_launch("gemm_tcgen05_pair");
 }
 
@@ -392,4 +397,17 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
   }
   if (out_dtype == HFEE_BF16) return launch_pair<EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   return launch_pair<EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
+}
+
+// The q/k/v product with rotation and cache write in its epilogue (hfee_gemm_tcgen05_rope) on pairs of
+// CTAs; called by that entry point, which has checked the arguments, for shapes with at least two
+// rounds of 256 x 256 tiles.
+int hfee_gemm_pair_rope(const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
+                        const tc::RopeEpi& rope, int* status, cudaStream_t stream) {
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc != HFEE_OK) return rc;
+  rc = make_map(&mw, W, N, K, ldw, BNH);
+  if (rc != HFEE_OK) return rc;
+  return launch_pair<EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, stream, rope);
 }
