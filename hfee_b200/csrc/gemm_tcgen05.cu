@@ -498,7 +498,7 @@ HFEE_API int hfee_gemm_tcgen05_stream_k(int M, int N, int K, int block_n, long l
 }
 
 int hfee_gemm_pair_rope(const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-                        const tc::RopeEpi& rope, int* status, cudaStream_t stream);      // gemm_tcgen05_pair.cu
+                        const tc::RopeEpi& rope, int block_n, int* status, cudaStream_t stream);      // gemm_tcgen05_pair.cu
 
 // 1 if hfee_gemm_tcgen05_rope takes these head sizes (bfloat16 implied): heads of 64 or 128 dims, all
 // of them rotated.
@@ -539,7 +539,14 @@ HFEE_API int hfee_gemm_tcgen05_rope(const void* A, long long lda, const void* W,
   // pairs of CTAs on tiles of 256 x 256 where those make two rounds or more (the q/k/v product of the
   // benchmark model at 2,048 tokens has 96 of them for 74 pairs: the single-CTA tiles fill the SMs better)
   if (sms > 0 && M > BM && (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= 2 * (sms / 2))
-    return hfee_gemm_pair_rope(A, lda, W, ldw, M, N, K, rope, status, stream);
+    return hfee_gemm_pair_rope(A, lda, W, ldw, M, N, K, rope, 256, status, stream);
+  if (sms > 0 && M > BM && head_dim == 64 && N % 192 == 0) {
+    // pairs on tiles of 256 x 192 (three heads) where those fill their rounds to four fifths or more: the
+    // q/k/v product of the benchmark model at 2,048 tokens has 128 of them for 74 pairs (prompt pass 3.76 -> 3.69 ms)
+    const long long pairs = sms / 2, tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * (N / 192);
+    const long long rounds = (tiles + pairs - 1) / pairs;
+    if (tiles * 5 >= rounds * pairs * 4) return hfee_gemm_pair_rope(A, lda, W, ldw, M, N, K, rope, 192, status, stream);
+  }
   int bn = tiles_256 >= 96 || sms <= 0 ? 256 : 128;
   if (bn == 256 && head_dim == 64 && sms > 0) {
     // three heads wide where that saves a round of tiles (16 x 12 tiles of 256 are two rounds on 148 SMs

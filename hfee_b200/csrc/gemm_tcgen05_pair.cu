@@ -26,17 +26,19 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128;               // rows of A per CTA; a pair covers 256
-constexpr int BN = 256;               // columns of the tile; each CTA loads 128 rows of W
-constexpr int BNH = BN / 2;
+// columns of a tile: 256, or 192 for the q/k/v product of 64-dim heads where three heads per tile save a round
 constexpr int THREADS = 320;
 constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
-constexpr int W_BYTES = BNH * BK * 2;         // 16 KB
-constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
 constexpr int EPI_BYTES = EPI_WARPS * 32 * 128;
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
+template <int BN> struct PairCfg {
+  static constexpr int BNH = BN / 2;                    // rows of W each CTA loads
+  static constexpr int W_BYTES = BNH * BK * 2;          // 16 KB (12 KB)
+  static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
+};
 
 enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
 
@@ -79,11 +81,12 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
 }
 
-template <int EPI, typename TOut>
+template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_c, int reduce_by_tma,
                  TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status, const RopeEpi rope) {
+  constexpr int BNH = PairCfg<BN>::BNH, STAGE_BYTES = PairCfg<BN>::STAGE_BYTES;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];         // used in the even CTA: both CTAs' loads of a stage
   __shared__ __align__(8) uint64_t empty_bar[STAGES];        // in each CTA: the MMAs that read the stage are done
@@ -325,7 +328,7 @@ int make_map_c(CUtensorMap* map, void* base, long long rows, long long cols, lon
   return HFEE_OK;
 }
 
-template <int EPI, typename TOut>
+template <int BN, int EPI, typename TOut>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
                 cudaStream_t stream, const RopeEpi& rope = RopeEpi{}) {
   CUtensorMap mc = ma;
@@ -337,8 +340,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05_pair: cannot get %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<BN>::SMEM);
+    if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "gemm_tcgen05_pair: cannot get %d bytes of shared memory: %s", PairCfg<BN>::SMEM, cudaGetErrorString(e));
     configured = true;
   }
   const int sms = hfee_sm_count();
@@ -348,7 +351,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = SMEM;
+  cfg.dynamicSmemBytes = PairCfg<BN>::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[3];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -363,7 +366,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long
     attr[2].val.sharedMemCarveout = (unsigned int)carve;
     cfg.numAttrs = 3;
   }
-  cudaLaunchKernelEx(&cfg, gemm_pair_kernel<EPI, TOut>, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status, rope);
+  cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN, EPI, TOut>, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status, rope);
   return hfee_check_launch("gemm_tcgen05_pair");
 }
 
@@ -385,29 +388,30 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc != HFEE_OK) return rc;
-  rc = make_map(&mw, W, N, K, ldw, BNH);
+  rc = make_map(&mw, W, N, K, ldw, 128);
   if (rc != HFEE_OK) return rc;
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: accumulate needs a float32 output");
-    return launch_pair<EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, stream);
+    return launch_pair<256, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, stream);
   }
   if (epilogue == EPI_SWIGLU) {
     if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue writes bfloat16");
-    return launch_pair<EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+    return launch_pair<256, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   }
-  if (out_dtype == HFEE_BF16) return launch_pair<EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
-  return launch_pair<EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
+  if (out_dtype == HFEE_BF16) return launch_pair<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+  return launch_pair<256, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
 }
 
 // The q/k/v product with rotation and cache write in its epilogue (hfee_gemm_tcgen05_rope) on pairs of
 // CTAs; called by that entry point, which has checked the arguments, for shapes with at least two
-// rounds of 256 x 256 tiles.
+// rounds of 256 x 256 tiles, or with tiles of 256 x 192 (block_n = 192, heads of 64 dims).
 int hfee_gemm_pair_rope(const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-                        const tc::RopeEpi& rope, int* status, cudaStream_t stream) {
+                        const tc::RopeEpi& rope, int block_n, int* status, cudaStream_t stream) {
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc != HFEE_OK) return rc;
-  rc = make_map(&mw, W, N, K, ldw, BNH);
+  rc = make_map(&mw, W, N, K, ldw, block_n / 2);
   if (rc != HFEE_OK) return rc;
-  return launch_pair<EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, stream, rope);
+  if (block_n == 192) return launch_pair<192, EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, stream, rope);
+  return launch_pair<256, EPI_ROPE, __nv_bfloat16>(ma, mw, nullptr, 0, M, N, K, status, stream, rope);
 }
