@@ -140,6 +140,23 @@ def test_first_tokens_of_a_sequence(tiny_dirs):
             assert np.abs(row - ref[t]).max() / np.abs(ref[t]).max() < tol, (dtype, t)
 
 
+def test_long_prompts_in_equal_portions_beside_decoding_requests_replay_graphs(tiny_dirs):
+    """Ten requests with prompts of 70 to 120 tokens, four at a time, prompts cut into portions of 32: the
+    shapes of the mixed steps repeat and are replayed from CUDA graphs; every token equals the plain
+    implementation's."""
+    from hfee_b200 import Engine, SamplingOptions
+    cfg, w = plain.load_model_dir(tiny_dirs["B"])
+    prompts = prompts_for(cfg, (70, 96, 120, 75, 100, 88, 111, 97, 105, 80), seed=13)
+    want = [plain.greedy_generate(cfg, w, p, 8) for p in prompts]
+    eng = Engine(tiny_dirs["B"], dtype="float32", page_size=16, max_requests=4, max_context=160,
+                 max_batch_tokens=64, prefill_chunk=32)
+    assert eng.config.use_cuda_graphs
+    res = eng.generate(prompts, SamplingOptions.greedy(num_predict=8))
+    assert [r.token_ids for r in res] == want
+    shapes = [k for k in eng.runner._graphs if isinstance(k, tuple)]
+    assert shapes and eng.runner.graph_replays > 0, (shapes, eng.runner.graph_replays)
+
+
 def test_preemption_under_a_tiny_cache_changes_no_token(tiny_dirs):
     from hfee_b200 import Engine, SamplingOptions
     cfg, w = plain.load_model_dir(tiny_dirs["A"])
