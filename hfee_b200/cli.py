@@ -176,9 +176,9 @@ def cmd_show(argv: List[str]) -> int:
     ap = argparse.ArgumentParser(prog="hfee-b200 show")
     ap.add_argument("model")
     a = ap.parse_args(argv)
-    from .config import read_config_json, resolve
+    from .config import resolve_model_dir
     from .parts.model import model_tensor_needs
-    arch, cfg = resolve(read_config_json(a.model))
+    arch, cfg = resolve_model_dir(a.model)
     spec = arch.build_spec(cfg)
     params = 0
     for need in model_tensor_needs(spec).values():

@@ -13,7 +13,7 @@ from typing import Any, List, Optional, Sequence
 import torch
 
 from ..cache import CacheManager, OutOfPages
-from ..config import EngineConfig, read_config_json, resolve
+from ..config import EngineConfig, resolve_model_dir
 from ..parts import DecoderModel, Runtime
 from ..weights import Checkpoint
 from .batch import Step, StepBuffers, StepEntry
@@ -40,7 +40,7 @@ class ModelRunner:
     def __init__(self, model_dir: str, engine: Optional[EngineConfig] = None):
         self.engine = engine or EngineConfig()
         e = self.engine
-        self.arch, self.config = resolve(read_config_json(model_dir))
+        self.arch, self.config = resolve_model_dir(model_dir)
         self.spec = self.arch.build_spec(self.config)
         self.device = torch.device(e.device)
         self.rt = Runtime(_DTYPES[e.dtype], self.device, e.max_batch_tokens, e.max_requests, e.page_size)

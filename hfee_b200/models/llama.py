@@ -47,4 +47,16 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     )
 
 
-register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_spec)
+def llama_sizes_from_tensors(config_json, shapes):
+    """``intermediate_size`` from the rows of the first layer's gate projection when config.json
+    leaves it out (hostfog/hfee internal/llm/model.go:146-148 takes the feed-forward's width from the gate
+    matrix in the same way)."""
+    if "intermediate_size" in config_json:
+        return config_json
+    gate = shapes.get("model.layers.0.mlp.gate_proj.weight")
+    if gate is None or len(gate) != 2:
+        return config_json          # the typed configuration will name the missing key
+    return {**config_json, "intermediate_size": int(gate[0])}
+
+
+register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_spec, llama_sizes_from_tensors)

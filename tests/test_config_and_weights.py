@@ -138,6 +138,25 @@ def test_buffers_the_architecture_names_as_ignorable_are_skipped_with_a_warning(
     assert e.value.unexpected == ["model.layers.0.self_attn.something_else"]
 
 
+def test_a_config_without_the_feed_forward_width_takes_it_from_the_gate_projection(tmp_path):
+    """config.json without ``intermediate_size``: a model folder's width comes from the rows of the first
+    layer's gate matrix (as the reference reads it); the content of config.json alone still names the key."""
+    import json
+    from hfee_b200.config import resolve, resolve_model_dir
+    d = str(tmp_path / "m")
+    write_random_model(d, TINY_A, seed=0)
+    short = {k: v for k, v in TINY_A.items() if k != "intermediate_size"}
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(short, f)
+    arch, cfg = resolve_model_dir(d)
+    assert cfg.intermediate_size == TINY_A["intermediate_size"]
+    assert cfg == resolve(TINY_A)[1]
+    with pytest.raises(ConfigError, match="intermediate_size"):
+        resolve(short)
+    spec = arch.build_spec(cfg)
+    Checkpoint(d).check(model_tensor_needs(spec), spec.ignorable)          # and the checkpoint fits it
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     d = str(tmp_path / "m")
     write_random_model(d, TINY_A, seed=0)
