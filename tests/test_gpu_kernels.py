@@ -117,7 +117,9 @@ def test_rope_cache_write(ops, dtype, heads, kv, hd, rope_dim, inter):
                                                        (32, 8, 64, False, 2048, 2048, 64), (6, 2, 64, False, 1100, 520, 64),
                                                        # enough tiles of 256 x 256 for the pairs of CTAs to take over
                                                        (32, 8, 128, False, 2048, 256, 64), (40, 40, 128, True, 600, 192, 64),
-                                                       (48, 16, 64, False, 1500, 128, 32)])
+                                                       (48, 16, 64, False, 1500, 128, 32),
+                                                       # 224 single-CTA tiles of three heads (192 columns) in two rounds
+                                                       (32, 8, 64, False, 1792, 128, 64)])
 @pytest.mark.parametrize("with_cache", [True, False])
 def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(ops, heads, kv, hd, inter, n, k, page, with_cache):
     """Token rows that do not fill the last tile of 128, head counts that do not fill the last tile of
