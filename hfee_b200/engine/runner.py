@@ -22,11 +22,13 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 # A decode step is a chain of short kernels, and an SM changes its split between shared memory and L1
 # only when it is empty: the kernels of such a step all ask for one split (percent of the shared-memory
 # maximum).  Measured, benchmark model, ms per step against the driver's per-kernel choice: 58 % at
-# batch 2 / 4 / 8 / 16 / 32: 0.752 / 0.806 / 0.833 / 1.043 / 1.394 against 0.761 / 0.818 / 0.861 /
-# 1.064 / 1.404 (more shared memory than that starves the kernels that stream weights through L1: 100 %
-# at batch 8 takes 1.135); at batch 64, where attention is half the step and wants three CTAs of 76 KB
-# per SM, 100 % takes 1.78 against 1.85.  A prompt of 2,048 tokens: 4.29 ms at 58 % against 4.35.
-STEP_CARVEOUT, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 48
+# batch 2 / 4 / 8 / 16: 0.752 / 0.806 / 0.833 / 1.043 against 0.761 / 0.818 / 0.861 / 1.064 (more
+# shared memory than that starves the kernels that stream weights through L1: 100 % at batch 8 takes
+# 1.135, at batch 16 1.46).  From 17 requests on the products run on tcgen05 with rings of 200 KB and the
+# attention wants three CTAs of 76 KB per SM: 100 % at batch 17 / 20 / 24 / 40 / 48 / 64: 1.096 / 1.154 /
+# 1.270 / 1.488 / 1.606 / 1.78 against 1.144 / 1.279 / 1.333 / 1.575 / 1.654 / 1.85 at 58 % (batch 32 and 36
+# are within 1 % either way).  A prompt of 2,048 tokens: 4.29 ms at 58 % against 4.35.
+STEP_CARVEOUT, DECODE_CARVEOUT_MANY, DECODE_MANY_REQUESTS = 58, 100, 17
 # Steps of up to this many tokens are replayed from CUDA graphs once their shape has been seen twice: the
 # host needs about 2 ms to launch a pass of a 16-layer model whatever its size, the GPU less than that
 # below about 1,000 tokens.  At most GRAPH_LIMIT graphs are kept.
